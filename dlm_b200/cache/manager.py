@@ -1,0 +1,152 @@
+"""The cache of a model: page pools with their tensors, state slots, step metadata.
+
+Bookkeeping (which page belongs to whom) is native code (``csrc/host``); this
+module owns the device tensors the ids index and turns a list of
+``(request slot, tokens, wanted places)`` into the device-side ``StepBatch``.
+
+Layout of a call's keys (values alike): ``[pages + 1, kv_heads, page_size,
+head_dim]``; a page of one kv head is a contiguous ``page_size x head_dim`` tile.
+The last page is a sink that padded rows write to; the pool never hands it out.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..build import load_host
+from ..parts.base import GroupView, PagedView, StepBatch
+
+
+class ModelCache:
+    def __init__(self, model, *, page_size: int = 64, num_pages: int | None = None, max_tokens: int | None = None,
+                 num_slots: int = 64):
+        """``num_pages`` pages per group, or enough for ``max_tokens`` tokens held at once."""
+        host = load_host()
+        self.host = host
+        rt = model.rt
+        self.rt = rt
+        self.page_size = int(page_size)
+        if num_pages is None:
+            if max_tokens is None:
+                raise ValueError("give num_pages or max_tokens")
+            num_pages = -(-int(max_tokens) // self.page_size)
+        self.num_pages = int(num_pages)
+        self.num_slots = int(num_slots)
+        needs = model.cache_needs()
+        # groups: one per distinct window among the calls that own paged keys/values
+        self.group_windows: list[int] = []
+        self.call_group: dict[int, int] = {}
+        self.call_owner: dict[int, int] = {}
+        self.k: dict[int, torch.Tensor] = {}
+        self.v: dict[int, torch.Tensor] = {}
+        self.state: dict[int, torch.Tensor] = {}
+        for ci, (kv, st, owner) in enumerate(needs):
+            self.call_owner[ci] = owner
+            if kv is not None and owner == ci:
+                w = int(kv.window or 0)
+                if w not in self.group_windows:
+                    self.group_windows.append(w)
+                self.call_group[ci] = self.group_windows.index(w)
+                shape = (self.num_pages + 1, kv.num_kv_heads, self.page_size, kv.head_dim)
+                self.k[ci] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+                self.v[ci] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+            if st is not None:
+                self.state[ci] = torch.zeros((self.num_slots, *st.shape), dtype=st.dtype, device=rt.device)
+        for ci, (kv, st, owner) in enumerate(needs):
+            if kv is not None and owner != ci:
+                self.call_group[ci] = self.call_group[owner]
+        if not self.group_windows:
+            self.group_windows.append(0)     # a model without paged caches still counts tokens
+        self.manager = host.CacheManager(
+            [host.GroupSpec(self.page_size, w, self.num_pages) for w in self.group_windows], self.num_slots)
+        self._pinned = []
+        self._ring = 0
+
+    # ------------------------------------------------------------ requests
+    def open(self) -> int:
+        """Takes a state slot for a new request (its per-request state is zeroed).  -1: none free."""
+        slot = self.manager.open()
+        if slot >= 0:
+            self.reset_state(slot)
+        return slot
+
+    def reset_state(self, slot: int) -> None:
+        """Zeroes the per-request state of a slot (a request starts, or starts over)."""
+        for t in self.state.values():
+            t[slot].zero_()
+
+    def close(self, slot: int) -> None:
+        self.manager.close(slot)
+
+    def append(self, slot_and_n) -> None:
+        self.manager.append(list(slot_and_n))
+
+    def bytes_per_token(self) -> int:
+        return sum(2 * k.shape[1] * k.shape[3] * k.element_size() for k in self.k.values())
+
+    # ---------------------------------------------------------- step views
+    def paged_view(self, call: int, batch: StepBatch):
+        if call not in self.call_group:
+            return None
+        owner = self.call_owner[call]
+        return PagedView(self.k[owner], self.v[owner], batch.groups[self.call_group[call]], write=(owner == call))
+
+    def state_tensor(self, call: int):
+        return self.state.get(call)
+
+    # ------------------------------------------------------------ metadata
+    def _staging(self, n: int):
+        """A pinned int32 buffer that no copy still in flight reads (ring of four)."""
+        if self.rt.device.type != "cuda":
+            return torch.empty(n, dtype=torch.int32), None
+        if not self._pinned:
+            self._pinned = [[torch.empty(max(n, 4096), dtype=torch.int32).pin_memory(), None] for _ in range(4)]
+        self._ring = (self._ring + 1) % len(self._pinned)
+        ent = self._pinned[self._ring]
+        if ent[1] is not None:
+            ent[1].synchronize()
+        if ent[0].numel() < n:
+            ent[0] = torch.empty(max(n, 2 * ent[0].numel()), dtype=torch.int32).pin_memory()
+        return ent[0], ent
+
+    def make_batch(self, items, fixed_table_width: int = 0, into: torch.Tensor | None = None) -> StepBatch:
+        """``items``: list of ``(slot, tokens, want)``; the requests' lengths must already
+        include these tokens (``append`` first).  ``into``: a device int32 buffer to reuse
+        (replayed graphs); its layout must not change between calls."""
+        host = self.host
+        sitems = [host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
+        lay = self.manager.plan_layout(sitems, fixed_table_width)
+        stage, ent = self._staging(lay.total)
+        self.manager.pack(sitems, lay, stage.data_ptr(), stage.numel())
+        if into is not None:
+            if into.numel() < lay.total:
+                raise ValueError("metadata buffer too small")
+            into[:lay.total].copy_(stage[:lay.total], non_blocking=True)
+            dev = into
+        else:
+            dev = stage[:lay.total].to(self.rt.device, non_blocking=True)
+        if ent is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            ent[1] = ev
+        return self.batch_from_layout(lay, dev)
+
+    def batch_from_layout(self, lay, dev: torch.Tensor) -> StepBatch:
+        T, R, N = lay.num_tokens, lay.num_requests, lay.num_wanted
+
+        def sl(off, n):
+            return dev[off:off + n]
+
+        groups = []
+        for g, w in enumerate(self.group_windows):
+            width = lay.table_width[g]
+            groups.append(GroupView(slots=sl(lay.off_slots[g], T),
+                                    block_table=sl(lay.off_table[g], R * width).view(R, width),
+                                    page_size=self.page_size, window=w))
+        return StepBatch(num_tokens=T, num_requests=R, tokens=sl(lay.off_tokens, T),
+                         positions=sl(lay.off_positions, T), token_req=sl(lay.off_token_req, T),
+                         cu_q=sl(lay.off_cu_q, R + 1), kv_len=sl(lay.off_kv_len, R),
+                         state_slot=sl(lay.off_state_slot, R), logit_rows=sl(lay.off_logit_rows, N),
+                         groups=groups, max_q_len=lay.max_q_len, max_kv_len=lay.max_kv_len)
+
+    def stats(self):
+        return [self.manager.stats(g) for g in range(len(self.group_windows))]

@@ -1,0 +1,75 @@
+// Launchers of every kernel.  All pointers are device pointers; `stream` is the
+// CUDA stream to launch on.  dtype: 0 = float32, 1 = bfloat16 (dlmk::DType).
+// Launchers validate sizes and throw std::invalid_argument for what a kernel
+// cannot take; none of them allocates memory.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace dlmk {
+
+enum Epilogue : int {
+    EPI_STORE = 0,    // out[m, n] = acc (+ bias[n]), stored as the output dtype
+    EPI_ADD = 1,      // out[m, n] += acc, out is float32 (the residual stream)
+    EPI_SWIGLU = 2    // out[m, n/2] = silu(acc[m, n]) * acc[m, n+1] for even n (interleaved weight rows)
+};
+
+// out[T, H] (f32) = table[tokens[t], :]
+void embed(const int32_t* tokens, const void* table, float* out, int T, int H, int V, int dtype, cudaStream_t stream);
+
+// out[i, :] = x[rows ? rows[i] : i, :] * rsqrt(mean(x^2) + eps) * w      (x, w f32; out dtype given)
+void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int n_rows, int H, float eps,
+             int out_dtype, cudaStream_t stream);
+
+// C[M, N] = A[M, K] · W[N, K]^T with an epilogue.  Dense: expert_offsets == nullptr.
+// Grouped: rows [expert_offsets[e], expert_offsets[e+1]) use W + e * w_expert_stride elements.
+// a_rows (optional) gathers the rows of A: row m of the product reads A[a_rows[m], :].
+// `fast` != 0 allows tensor-core kernels (bfloat16 inputs only); 0 forces the plain FMA kernel.
+void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
+          const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N, int K,
+          int in_dtype, int out_dtype, int epilogue, int fast, cudaStream_t stream);
+
+// Rotates q and k heads of qkv[T, (nh + 2 nkv) * hd] (f32) by position * inv_freq (split-half pairs within the
+// first rotary_dim dims; inv_freq == nullptr: no rotation), writes q to q_out[T, nh * hd] and, where
+// slots != nullptr and slots[t] >= 0, k and v to the paged caches [pages, nkv, page_size, hd].
+void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim,
+                   const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int T, int nh, int nkv, int hd,
+                   int page_size, int total_pages, int dtype, cudaStream_t stream);
+
+// Causal (optionally windowed) attention of every token of the step over its request's paged keys and values.
+void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
+               const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
+               int page_size, int total_pages, int window, float scale, int max_q_len, int max_kv_len, int dtype,
+               int fast, cudaStream_t stream);
+
+// Router: logits = h · w^T (32-bit), softmax over E, top-k (ties: lower index), optional renormalisation.
+// has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).
+void router_topk(const void* h, const void* w, int32_t* ids, float* wts, float* gate, int T, int H, int E, int k,
+                 int norm, int has_gate, int dtype, cudaStream_t stream);
+
+// Groups the n = T * k (token, choice) pairs by expert: offsets[E + 1], rows[n] = token of each sorted row,
+// dest[n] = sorted row of pair (t, j).
+void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int32_t* rows, int32_t* dest,
+                 cudaStream_t stream);
+
+// resid[t, :] += sum_j wts[t, j] * y[dest[t, j], :] (+ gate[t] * shared[t, :]); gate == nullptr: 1.
+void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
+                 float* resid, int T, int H, int k, cudaStream_t stream);
+
+// out[i] = index of the first maximum of logits[i, :]
+void argmax(const float* logits, int32_t* out, int N, int V, cudaStream_t stream);
+
+// Per row: repetition penalty over seen tokens, then greedy (temperature <= 0) or temperature / top-k / top-p /
+// min-p sampling with the uniform number u[i] (candidates ordered by logit descending, ties by index).
+// seen_offsets[N + 1] indexes seen_tokens; params[i] = {temperature, top_p, min_p, repetition_penalty}; top_k[i].
+// scratch: N * V floats.
+void sample(const float* logits, int32_t* out, int N, int V, const float* params, const int32_t* top_k,
+            const float* u, const int32_t* seen_offsets, const int32_t* seen_tokens, float* scratch,
+            cudaStream_t stream);
+
+// A device-side error flag kernels set instead of touching memory they must not (a page id outside the pool,
+// an expert id outside the table).  Returns the flag and clears it.
+int take_error_flag();
+
+}  // namespace dlmk

@@ -1,0 +1,193 @@
+// Memory-bound kernels: embedding gather, RMSNorm, rotary + paged key/value write,
+// combination of expert outputs into the residual.
+#include "api.h"
+#include "common.cuh"
+
+namespace dlmk {
+
+// ------------------------------------------------------------------ error flag
+namespace {
+int* g_flag_host = nullptr;
+int* g_flag_dev = nullptr;
+}  // namespace
+
+// Device pointer of a host-mapped flag (allocated once per process, at the first launch that needs it).
+int* error_flag_ptr() {
+    if (g_flag_dev == nullptr) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&g_flag_host), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+            cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_flag_dev), g_flag_host, 0) != cudaSuccess)
+            throw std::runtime_error("dlm_b200 kernels: cannot allocate the error flag");
+        *g_flag_host = 0;
+    }
+    return g_flag_dev;
+}
+
+int take_error_flag() {
+    if (g_flag_host == nullptr) return 0;
+    int v = *reinterpret_cast<volatile int*>(g_flag_host);
+    *reinterpret_cast<volatile int*>(g_flag_host) = 0;
+    return v;
+}
+
+// ------------------------------------------------------------------- embedding
+namespace {
+
+template <typename T>
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out,
+                             int H, int V, int* err) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* o = out + (long long)t * H;
+    if (tok < 0 || tok >= V) {   // never read outside the table
+        if (threadIdx.x == 0) *err = 1;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const T* row = table + (long long)tok * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// ---------------------------------------------------------------------- rmsnorm
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ out,
+                               const int32_t* __restrict__ rows, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* xr = x + (long long)(rows ? rows[r] : r) * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TOut* o = out + (long long)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TOut>((xr[i] * inv) * w[i]);
+}
+
+// ------------------------------------------------------- rotary + cache write
+// One block per token; threads run over (head, pair) of q, then k, then v elements.
+template <typename T>
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                     const float* __restrict__ inv_freq, int rotary_dim,
+                                     const int32_t* __restrict__ slots, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                     T* __restrict__ v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
+                                     int* err) {
+    const int t = blockIdx.x;
+    const int Q = nh * hd, KV = nkv * hd;
+    const float* row = qkv + (long long)t * (Q + 2 * KV);
+    const float pos = (float)positions[t];
+    const int half = rotary_dim / 2;
+    long long kv_base = -1;   // element offset of (page, head 0, offset-in-page, 0)
+    int in_page = 0, page = -1;
+    if (slots != nullptr) {
+        const int s = slots[t];
+        if (s >= 0) {
+            page = s / page_size;
+            in_page = s % page_size;
+            if (page >= total_pages) {
+                if (threadIdx.x == 0) *err = 2;
+                page = -1;
+            }
+        }
+    }
+    // q heads and k heads: rotate
+    const int rot_heads = nh + nkv;
+    for (int idx = threadIdx.x; idx < rot_heads * hd; idx += blockDim.x) {
+        const int h = idx / hd, d = idx % hd;
+        const float* src = row + (long long)h * hd;    // q heads then k heads are contiguous in qkv
+        float val;
+        if (inv_freq != nullptr && d < rotary_dim) {
+            const int i = d < half ? d : d - half;
+            const float ang = pos * inv_freq[i];
+            float s, c;
+            sincosf(ang, &s, &c);
+            const float a = src[i], b = src[i + half];
+            val = d < half ? (a * c - b * s) : (a * s + b * c);
+        } else {
+            val = src[d];
+        }
+        if (h < nh) {
+            q_out[(long long)t * Q + idx] = from_f32<T>(val);
+        } else if (page >= 0) {
+            const int kh = h - nh;
+            k_cache[(((long long)page * nkv + kh) * page_size + in_page) * hd + d] = from_f32<T>(val);
+        }
+    }
+    if (page >= 0) {
+        const float* vsrc = row + Q + KV;
+        for (int idx = threadIdx.x; idx < KV; idx += blockDim.x) {
+            const int kh = idx / hd, d = idx % hd;
+            v_cache[(((long long)page * nkv + kh) * page_size + in_page) * hd + d] = from_f32<T>(vsrc[idx]);
+        }
+    }
+    (void)kv_base;
+}
+
+// ------------------------------------------------------------------ moe combine
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ dest,
+                                   const float* __restrict__ wts, const float* __restrict__ shared,
+                                   const float* __restrict__ gate, float* __restrict__ resid, int H, int k) {
+    const int t = blockIdx.x;
+    float* r = resid + (long long)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < k; ++j)
+            acc = fmaf(wts[t * k + j], y[(long long)dest[t * k + j] * H + i], acc);
+        if (shared != nullptr) {
+            const float g = gate ? gate[t] : 1.0f;
+            acc = fmaf(g, shared[(long long)t * H + i], acc);
+        }
+        r[i] += acc;
+    }
+}
+
+}  // namespace
+
+int* error_flag_ptr();
+
+void embed(const int32_t* tokens, const void* table, float* out, int T, int H, int V, int dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    int* err = error_flag_ptr();
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == F32) embed_kernel<float><<<T, threads, 0, stream>>>(tokens, static_cast<const float*>(table), out, H, V, err);
+    else embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, static_cast<const __nv_bfloat16*>(table), out, H, V, err);
+    check_launch("embed");
+}
+
+void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int n_rows, int H, float eps,
+             int out_dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (out_dtype == F32) rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, static_cast<float*>(out), rows, H, eps);
+    else rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, static_cast<__nv_bfloat16*>(out), rows, H, eps);
+    check_launch("rmsnorm");
+}
+
+void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim,
+                   const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int T, int nh, int nkv, int hd,
+                   int page_size, int total_pages, int dtype, cudaStream_t stream) {
+    if (T <= 0) return;
+    DLM_CHECK(inv_freq == nullptr || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= hd),
+              "rope: rotary_dim must be even and in 2..head_dim");
+    int* err = error_flag_ptr();
+    const int threads = 256;
+    if (dtype == F32)
+        rope_kv_write_kernel<float><<<T, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+            static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), nh, nkv, hd,
+            page_size, total_pages, err);
+    else
+        rope_kv_write_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+            static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+            static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
+    check_launch("rope_kv_write");
+}
+
+void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
+                 float* resid, int T, int H, int k, cudaStream_t stream) {
+    if (T <= 0) return;
+    moe_combine_kernel<<<T, 256, 0, stream>>>(y, dest, wts, shared, gate, resid, H, k);
+    check_launch("moe_combine");
+}
+
+}  // namespace dlmk

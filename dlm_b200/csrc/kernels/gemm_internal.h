@@ -1,0 +1,14 @@
+// Kernels behind dlmk::gemm (see api.h for the meaning of the arguments).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace dlmk {
+
+// FMA-unit kernel: any sizes, both dtypes.
+void gemm_simt(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
+               const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
+               int K, int in_dtype, int out_dtype, int epilogue, cudaStream_t stream);
+
+}  // namespace dlmk

@@ -1,0 +1,188 @@
+"""The engine: a model, its cache, one step function, a scheduler and a sampler.
+
+``Engine.from_pretrained(dir)`` mirrors the reference's ``load_generator``
+(src/loader.rs:340-346) and ``Engine.generate(prompt, ...)`` its
+``Generator::generate(prompt, GenerationConfig)`` (src/generate.rs:338-373):
+same option names, same defaults (16 new tokens, greedy, no end-of-sequence
+token), the end-of-sequence token is part of the output.  Unlike the reference,
+several prompts are run together: prompts are cut into portions under a token
+budget and decoded tokens of other requests share the step.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Sequence
+
+import torch
+
+from ..build import load_host
+from ..cache import ModelCache
+from ..parts.base import Runtime
+from ..sampling import RequestSampler, SamplingParams, sample_rows
+from ..weights import load_model, random_model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _dtype(d) -> torch.dtype:
+    if d not in _DTYPES:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {d!r}")
+    return _DTYPES[d]
+
+
+def make_runtime(dtype="bfloat16", device="cuda:0", ops=None) -> Runtime:
+    """Runtime with the native kernels (the only product backend).  In 32-bit mode every
+    product and the attention run on the FMA units."""
+    dt = _dtype(dtype)
+    if ops is None:
+        from ..ops import native_ops
+        torch.cuda.set_device(torch.device(device))
+        ops = native_ops(fast=(dt == torch.bfloat16))
+    return Runtime(device, dt, ops)
+
+
+class Engine:
+    def __init__(self, config, model, *, page_size: int = 64, num_pages: int | None = None,
+                 max_tokens: int | None = None, max_requests: int = 64, max_step_tokens: int = 2048,
+                 max_context: int | None = None):
+        self.config, self.model, self.rt = config, model, model.rt
+        if max_context is None:
+            max_context = getattr(config, "max_position_embeddings", None) or 4096
+        self.max_context = int(max_context)
+        if num_pages is None and max_tokens is None:
+            max_tokens = min(self.max_context * max_requests, self._tokens_that_fit(page_size))
+        self.cache = ModelCache(model, page_size=page_size, num_pages=num_pages, max_tokens=max_tokens,
+                                num_slots=max_requests)
+        host = load_host()
+        self.scheduler = host.Scheduler(self.cache.manager, host.SchedulerConfig(
+            max_step_tokens=int(max_step_tokens), max_step_requests=int(max_requests),
+            max_context=self.max_context, vocab_size=int(model.spec.vocab_size)))
+        self._samplers: dict[int, RequestSampler] = {}
+        self._results: dict[int, list[int]] = {}
+        self._reasons: dict[int, str] = {}
+        self._next_id = 0
+        self.last_logits: torch.Tensor | None = None
+
+    # ------------------------------------------------------------ builders
+    @classmethod
+    def from_pretrained(cls, path: str, dtype="bfloat16", device="cuda:0", ops=None, **kw) -> "Engine":
+        rt = make_runtime(dtype, device, ops)
+        cfg, model = load_model(path, rt)
+        return cls(cfg, model, **kw)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0", ops=None, **kw) -> "Engine":
+        rt = make_runtime(dtype, device, ops)
+        cfg, model = random_model(config, seed, rt)
+        return cls(cfg, model, **kw)
+
+    def _tokens_that_fit(self, page_size: int) -> int:
+        per_token = 0
+        for kv, _, owner in self.model.cache_needs():
+            if kv is not None:
+                per_token += 2 * kv.num_kv_heads * kv.head_dim * (2 if self.rt.dtype == torch.bfloat16 else 4)
+        per_token = max(per_token // 1, 1)
+        if self.rt.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.rt.device)
+            budget = int(free * 0.6)
+        else:
+            budget = 1 << 28
+        return max(page_size, budget // per_token)
+
+    # ---------------------------------------------------------- step function
+    def step(self, items: Sequence[tuple[int, Sequence[int], Sequence[int]]]) -> torch.Tensor:
+        """Runs one batch.  ``items``: ``(slot, next tokens, wanted places)`` for each request
+        of the step; slots come from ``cache.open()``.  Takes the pages the tokens need,
+        runs only these tokens against the cache and returns the logits at the wanted
+        places, ``[wanted, vocab]`` in 32-bit, in the order of the items."""
+        self.cache.append([(s, len(t)) for s, t, _ in items])
+        return self._run(items)
+
+    def _run(self, items) -> torch.Tensor:
+        batch = self.cache.make_batch(items)
+        return self.model.step(batch, self.cache)
+
+    # ------------------------------------------------------------- generation
+    def submit(self, prompt: Iterable[int], params: SamplingParams | None = None, max_new_tokens: int = 16,
+               eos_token=None) -> int:
+        prompt = [int(t) for t in prompt]
+        rid = self._next_id
+        self._next_id += 1
+        eos = [] if eos_token is None else ([int(eos_token)] if isinstance(eos_token, int) else [int(t) for t in eos_token])
+        self.scheduler.submit(rid, prompt, int(max_new_tokens), eos)
+        self._samplers[rid] = RequestSampler(params or SamplingParams(), prompt)
+        return rid
+
+    def abort(self, rid: int) -> bool:
+        return self.scheduler.abort(rid)
+
+    def _deliver(self, finished) -> None:
+        for f in finished:
+            self._results[f.id] = list(f.output)
+            self._reasons[f.id] = f.reason
+            self._samplers.pop(f.id, None)
+
+    def run_step(self) -> list[tuple[int, int]]:
+        """One scheduler tick: plan, run, sample, commit.  Returns ``(request id, token)`` for
+        every token produced."""
+        sched = self.scheduler
+        plan = sched.plan()
+        if not plan.items:
+            fin = sched.drain_finished()
+            self._deliver(fin)
+            if not fin and not plan.preempted and sched.has_work():
+                raise RuntimeError("the scheduler could not place any request")
+            return []
+        for it in plan.items:
+            if it.start == 0:
+                self.cache.reset_state(it.slot)
+        items = [(it.slot, it.tokens, [len(it.tokens) - 1] if it.sample else []) for it in plan.items]
+        logits = self._run(items)
+        self.last_logits = logits
+        rows = [it for it in plan.items if it.sample]
+        tokens = sample_rows(self.rt.ops, logits, [self._samplers[it.id] for it in rows])
+        self.rt.ops.check_errors()
+        for it, tok in zip(rows, tokens):
+            self._samplers[it.id].note(tok)
+        self._deliver(sched.commit(plan, tokens))
+        return [(it.id, tok) for it, tok in zip(rows, tokens)]
+
+    def run(self) -> None:
+        while self.scheduler.has_work():
+            self.run_step()
+
+    def result(self, rid: int) -> list[int]:
+        return self._results.pop(rid)
+
+    def generate(self, prompts, max_new_tokens: int = 16, eos_token=None, temperature: float = 0.0,
+                 top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0, repetition_penalty: float = 1.0,
+                 seed: int = 0):
+        """Generates for one prompt (a list of token ids -> a list of token ids) or several
+        (a list of lists -> a list of lists).  Every request uses ``seed`` for its own
+        generator, so a prompt's output does not depend on what it was batched with."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        plist = [prompts] if single else list(prompts)
+        params = SamplingParams(temperature=temperature, top_p=top_p, top_k=top_k, min_p=min_p,
+                                repetition_penalty=repetition_penalty, seed=seed)
+        ids = [self.submit(p, SamplingParams(**vars(params)), max_new_tokens, eos_token) for p in plist]
+        self.run()
+        failed = [i for i in ids if self._reasons.get(i) == "cache"]
+        outs = [self.result(i) for i in ids]
+        if failed:
+            raise RuntimeError(f"{len(failed)} request(s) can never fit in the cache pool "
+                               f"({self.cache.num_pages} pages of {self.cache.page_size} tokens)")
+        return outs[0] if single else outs
+
+    def stats(self) -> dict:
+        st = self.scheduler.stats()
+        pools = self.cache.stats()
+        return {"steps": st.steps, "prompt_tokens": st.prompt_tokens, "decode_tokens": st.decode_tokens,
+                "preemptions": st.preemptions, "finished": st.finished,
+                "pages": [{"total": p.total_pages, "used": p.used_pages, "high_water": p.high_water} for p in pools]}
+
+
+def generate(model_path: str, prompts, dtype="bfloat16", device="cuda:0", **kw):
+    """Loads a model folder and generates (the shortest way from a folder to tokens)."""
+    eng_kw = {k: kw.pop(k) for k in ("page_size", "num_pages", "max_tokens", "max_requests", "max_step_tokens",
+                                     "max_context") if k in kw}
+    return Engine.from_pretrained(model_path, dtype=dtype, device=device, **eng_kw).generate(prompts, **kw)

@@ -1,0 +1,170 @@
+"""The kernel backend: thin, shape-checking wrappers around the sm_100a launchers.
+
+There is no other backend in the package and no fallback: constructing
+``NativeOps`` without a CUDA device, or without a kernel library that builds and
+loads, raises.  Every method takes and returns torch tensors on the CUDA device;
+outputs are allocated with torch's caching allocator (which is also what makes
+the calls capturable in a CUDA graph).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..build import load_kernels
+
+_F32, _BF16 = 0, 1
+
+
+def _dt(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise TypeError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _p(t: torch.Tensor | None) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class NativeOps:
+    """``fast=False`` keeps every product and the attention on the plain FMA kernels
+    (the path the 32-bit mode always takes)."""
+
+    def __init__(self, fast: bool = True):
+        if not torch.cuda.is_available():
+            raise KernelError("dlm_b200 needs a CUDA device: there is no CPU path")
+        self.k = load_kernels()
+        self.fast = 1 if fast else 0
+
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def check_errors(self) -> None:
+        """Raises if a kernel refused an access (page or token id outside its table)."""
+        flag = self.k.take_error_flag()
+        if flag:
+            what = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
+                    3: "a visible key has no page", 4: "expert id outside the table"}.get(flag, "unknown")
+            raise KernelError(f"a kernel reported error {flag}: {what}")
+
+    # ----------------------------------------------------------------- basic
+    def embed(self, tokens, table):
+        T, (V, H) = tokens.numel(), table.shape
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        self.k.embed(_p(tokens), _p(table), _p(out), T, H, V, _dt(table.dtype), self._stream())
+        return out
+
+    def rmsnorm(self, x, w, eps, out_dtype, rows=None):
+        H = x.shape[-1]
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, H), dtype=out_dtype, device=x.device)
+        self.k.rmsnorm(_p(x), _p(w), _p(out), _p(rows), n, H, float(eps), _dt(out_dtype), self._stream())
+        return out
+
+    # -------------------------------------------------------------- products
+    def _gemm(self, a, w, out, M, N, K, epilogue, *, bias=None, a_rows=None, offsets=None, num_experts=0,
+              w_expert_stride=0, ldo=None):
+        self.k.gemm(_p(a), a.stride(0), _p(a_rows), _p(w), K, w_expert_stride, _p(offsets), num_experts, _p(bias),
+                    _p(out), out.stride(0) if ldo is None else ldo, M, N, K, _dt(a.dtype), _dt(out.dtype), epilogue,
+                    self.fast, self._stream())
+
+    def linear(self, a, w, bias, out_dtype):
+        (M, K), N = a.shape, w.shape[0]
+        assert w.shape[1] == K and a.dtype == w.dtype
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        self._gemm(a, w, out, M, N, K, self.k.EPI_STORE, bias=bias)
+        return out
+
+    def linear_add(self, a, w, resid):
+        (M, K), N = a.shape, w.shape[0]
+        assert w.shape[1] == K and resid.shape == (M, N) and resid.dtype == torch.float32
+        self._gemm(a, w, resid, M, N, K, self.k.EPI_ADD)
+
+    def linear_swiglu(self, a, w_gate_up):
+        (M, K), N = a.shape, w_gate_up.shape[0]
+        out = torch.empty((M, N // 2), dtype=a.dtype, device=a.device)
+        self._gemm(a, w_gate_up, out, M, N, K, self.k.EPI_SWIGLU)
+        return out
+
+    def grouped_swiglu(self, a, w_gate_up, offsets, rows):
+        E, N, K = w_gate_up.shape
+        M = rows.numel()
+        out = torch.empty((M, N // 2), dtype=a.dtype, device=a.device)
+        self._gemm(a, w_gate_up, out, M, N, K, self.k.EPI_SWIGLU, a_rows=rows, offsets=offsets, num_experts=E,
+                   w_expert_stride=N * K)
+        return out
+
+    def grouped_linear(self, a, w, offsets):
+        E, N, K = w.shape
+        M = a.shape[0]
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        self._gemm(a, w, out, M, N, K, self.k.EPI_STORE, offsets=offsets, num_experts=E, w_expert_stride=N * K)
+        return out
+
+    # ------------------------------------------------------------- attention
+    def rope_kv_write(self, qkv, positions, inv_freq, rotary_dim, slots, k_cache, v_cache, nh, nkv, hd, out_dtype):
+        T = qkv.shape[0]
+        assert qkv.dtype == torch.float32 and qkv.shape[1] == (nh + 2 * nkv) * hd
+        total_pages, nkv_c, page_size, hd_c = k_cache.shape
+        assert (nkv_c, hd_c) == (nkv, hd) and k_cache.dtype == out_dtype
+        q = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
+        self.k.rope_kv_write(_p(qkv), _p(positions), _p(inv_freq), int(rotary_dim), _p(slots), _p(q), _p(k_cache),
+                             _p(v_cache), T, nh, nkv, hd, page_size, total_pages, _dt(out_dtype), self._stream())
+        return q
+
+    def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
+                  max_kv_len):
+        T = q.shape[0]
+        R, width = block_table.shape
+        total_pages, _, page_size, _ = k_cache.shape
+        out = torch.empty_like(q)
+        self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
+                         nh, nkv, hd, page_size, total_pages, int(window), float(scale), int(max_q_len),
+                         int(max_kv_len), _dt(q.dtype), self.fast, self._stream())
+        return out
+
+    # ------------------------------------------------------------------- moe
+    def router_topk(self, h, w, E, k, norm, has_gate):
+        T, H = h.shape
+        assert w.shape == (E + (1 if has_gate else 0), H)
+        ids = torch.empty((T, k), dtype=torch.int32, device=h.device)
+        wts = torch.empty((T, k), dtype=torch.float32, device=h.device)
+        gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
+        self.k.router_topk(_p(h), _p(w), _p(ids), _p(wts), _p(gate), T, H, E, k, int(norm), int(has_gate),
+                           _dt(h.dtype), self._stream())
+        return ids, wts, gate
+
+    def moe_permute(self, ids, E):
+        T, k = ids.shape
+        n = T * k
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=ids.device)
+        rows = torch.empty((n,), dtype=torch.int32, device=ids.device)
+        dest = torch.empty((T, k), dtype=torch.int32, device=ids.device)
+        self.k.moe_permute(_p(ids), n, k, E, _p(offsets), _p(rows), _p(dest), self._stream())
+        return offsets, rows, dest
+
+    def moe_combine(self, y, dest, wts, shared, gate, resid):
+        T, H = resid.shape
+        self.k.moe_combine(_p(y), _p(dest), _p(wts), _p(shared), _p(gate), _p(resid), T, H, dest.shape[1],
+                           self._stream())
+
+    # -------------------------------------------------------------- sampling
+    def argmax(self, logits):
+        N, V = logits.shape
+        out = torch.empty((N,), dtype=torch.int32, device=logits.device)
+        self.k.argmax(_p(logits), _p(out), N, V, self._stream())
+        return out
+
+    def sample(self, logits, params, top_k, u, seen_offsets, seen_tokens):
+        N, V = logits.shape
+        out = torch.empty((N,), dtype=torch.int32, device=logits.device)
+        scratch = torch.empty((N, V), dtype=torch.float32, device=logits.device)
+        self.k.sample(_p(logits), _p(out), N, V, _p(params), _p(top_k), _p(u), _p(seen_offsets), _p(seen_tokens),
+                      _p(scratch), self._stream())
+        return out
