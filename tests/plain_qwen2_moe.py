@@ -161,12 +161,20 @@ def route_topk(logits: torch.Tensor, k: int, norm: bool):
     return order, w
 
 
+# When a list, moe_ffn appends for every call the gap between the last chosen and the first
+# rejected expert's probability at each position (see PlainModel.router_margin).
+MARGIN_LOG = None
+
+
 def moe_ffn(x, lw, cfg: PlainConfig, rnd):
     """src/forward/cpu.rs:1005-1048: routed experts summed from zero in routing order, each
     scaled by its gate weight; then the shared expert scaled by sigmoid(gate·x) (1 when the
     gate tensor is absent)."""
     logits = x @ lw["router"].T
     ids, wts = route_topk(logits, cfg.k, cfg.norm_topk)
+    if MARGIN_LOG is not None and cfg.k < cfg.E:
+        sp = torch.sort(softmax(logits), dim=-1, descending=True).values
+        MARGIN_LOG.append(sp[:, cfg.k - 1] - sp[:, cfg.k])
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         acc = torch.zeros_like(x[t])
@@ -270,6 +278,27 @@ class PlainModel:
         for i in order:
             x = decoder_layer(x, self.layers[i], cfg, i, positions, self.inv_freq, self.rnd)
         return x
+
+    def router_margins(self, tokens) -> torch.Tensor:
+        """For every position, the smallest gap over the routed layers between the probability
+        of the last expert chosen and the first one rejected.  Top-k is discontinuous: where
+        this gap is within rounding, two correct implementations may route differently, and
+        everything after that position may differ; tests compare only up to there."""
+        global MARGIN_LOG
+        MARGIN_LOG = []
+        try:
+            self.hidden_states(tokens)
+            gaps = list(MARGIN_LOG)
+        finally:
+            MARGIN_LOG = None
+        if not gaps:
+            return torch.full((len(tokens),), float("inf"), dtype=torch.float64)
+        return torch.stack([g.to(torch.float64) for g in gaps]).min(dim=0).values
+
+    def clear_prefix(self, tokens, min_margin: float) -> int:
+        """Number of leading positions whose routing margin is at least ``min_margin``."""
+        low = torch.nonzero(self.router_margins(tokens) < min_margin)
+        return int(low[0]) if low.numel() else len(tokens)
 
     def logits(self, tokens, layer_order=None) -> torch.Tensor:
         """src/generate.rs:328-331 at every position: rmsnorm with model.norm, then the head.
