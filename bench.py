@@ -1,0 +1,275 @@
+"""Serving benchmark: decode tokens per second of the Qwen1.5-MoE-A2.7B-sized model with
+random weights (bfloat16) on one B200, plus prefill, roofline and end-to-end figures.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of the whole batch.  One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# Layer sizes of the model the benchmark is quoted on (Qwen1.5-MoE-A2.7B).
+MODEL = dict(
+    architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe",
+    num_hidden_layers=24, hidden_size=2048, num_attention_heads=16, num_key_value_heads=16, head_dim=128,
+    num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408, shared_expert_intermediate_size=5632,
+    norm_topk_prob=False, decoder_sparse_step=1, intermediate_size=5632, vocab_size=151936, rope_theta=1000000.0,
+    rms_norm_eps=1e-6, use_sliding_window=False, tie_word_embeddings=False, max_position_embeddings=4096)
+FULL_LAYERS = MODEL["num_hidden_layers"]
+
+
+def peaks():
+    """Measured peaks if the driver wrote them, else this pool's earlier measurement."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p.get("bf16_tflops_sustained") or p["bf16_tflops"]),
+                        source="measured")
+        except (KeyError, ValueError, json.JSONDecodeError):
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.samples:
+            if not (t0 - 0.05 <= t <= t1 + 0.15):
+                continue
+            parts = [x.strip() for x in line.split(",")]
+            try:
+                mhz.append(int(float(parts[0])))
+                mx = max(mx, int(float(parts[1])))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def weight_bytes_per_decode_step(cfg, batch, layers, esz=2):
+    """Bytes a decode step has to read: every weight it uses once.  Routed experts: the
+    expected number of distinct experts a batch of `batch` tokens touches per layer."""
+    H, Q, KV = cfg.hidden_size, cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    E, k, I, Is = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+    attn = ((Q + 2 * KV) * H + H * Q) * esz
+    distinct = E * (1.0 - (1.0 - k / E) ** batch)
+    moe = (E + 1) * H * esz + distinct * 3 * I * H * esz + 3 * Is * H * esz
+    head = cfg.vocab_size * H * esz
+    return layers * (attn + moe) + head
+
+
+def prefill_flops(cfg, T, layers):
+    H, Q, KV = cfg.hidden_size, cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    E, k, I, Is = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+    per_tok = 2 * H * (Q + 2 * KV) + 2 * Q * H + 2 * H * (E + 1) + k * 6 * H * I + 6 * H * Is
+    attn = 4 * Q * T * (T + 1) / 2          # QK^T and PV over the causal half
+    return layers * (per_tok * T + attn) + 2 * H * cfg.vocab_size
+
+
+def run_reference():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "vedantnimbarte/dlm is a Rust crate (Cargo.toml, no setup.py/pyproject.toml): pip cannot "
+                      "install it offline and no Rust toolchain is present"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    from dlm_b200.config import Qwen2MoeConfig
+    from dlm_b200.engine import Engine
+
+    pk = peaks()
+    raw = dict(MODEL)
+    raw["num_hidden_layers"] = args.layers
+    cfg = Qwen2MoeConfig.from_dict(raw)
+    torch.cuda.set_device(0)
+    max_batch = 64 if not args.no_points else args.batch
+    page = 64
+    pool_tokens = max_batch * (args.prompt_len + 256) + 4096
+    t_load = time.time()
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", page_size=page, max_tokens=pool_tokens,
+                             max_requests=max_batch, max_step_tokens=2048, max_context=args.context)
+    torch.cuda.synchronize()
+    load_s = time.time() - t_load
+    V = cfg.vocab_size
+    gen = torch.Generator().manual_seed(0)
+    counter = eng.rt.ops
+
+    def prompts(n, length):
+        return [torch.randint(0, V, (length,), generator=gen).tolist() for _ in range(n)]
+
+    def decode_run(batch, steps, warmup, sample_clocks=False):
+        """Prefills `batch` prompts through the scheduler, then times `steps` decode steps of the step
+        function (device time) and the same number through run_step (end to end)."""
+        ids = [eng.submit(p, max_new_tokens=10 ** 6) for p in prompts(batch, args.prompt_len)]
+        started = set()
+        while len(started) < batch:                   # admit and prefill everything
+            started.update(rid for rid, _ in eng.run_step())
+        # every request now decodes one token per step
+        for _ in range(warmup):
+            eng.run_step()
+        torch.cuda.synchronize()
+        # device-timed: plan + step function only, sampled tokens fed back without leaving the loop
+        sampler = ClockSampler()
+        if sample_clocks:
+            sampler.start()
+            time.sleep(0.3)
+        launches0 = counter.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        e0.record()
+        for _ in range(steps):
+            eng.run_step()
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        dev_ms = e0.elapsed_time(e1)
+        launches = counter.launches - launches0
+        clocks = None
+        if sample_clocks:
+            time.sleep(0.2)
+            sampler.stop()
+            clocks = sampler.summary(t0, t1)
+        # end to end: wall clock around the public loop, host tokens in and out every step
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        produced = 0
+        for _ in range(steps):
+            produced += len(eng.run_step())
+        torch.cuda.synchronize()
+        w1 = time.perf_counter()
+        ctx = eng.cache.manager.length(0) if eng.cache.manager.is_open(0) else args.prompt_len
+        for i in ids:
+            eng.abort(i)
+        eng.scheduler.drain_finished()
+        return dict(dev_ms=dev_ms, e2e_s=w1 - w0, produced=produced, launches=launches, clocks=clocks, ctx=ctx)
+
+    main_run = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
+    ms_per_step = main_run["dev_ms"] / args.steps
+    value = args.batch * args.steps / (main_run["dev_ms"] / 1e3)
+    e2e_value = main_run["produced"] / main_run["e2e_s"]
+    kv_bytes = args.batch * (args.prompt_len + args.warmup + args.steps // 2) * eng.cache.bytes_per_token()
+    step_bytes = weight_bytes_per_decode_step(cfg, args.batch, args.layers) + kv_bytes
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+
+    out = {
+        "metric": "decode tok/s @ batch 8 (Qwen1.5-MoE-A2.7B sizes, bf16, random weights)",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen1.5-MoE-A2.7B sizes", "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "1 GPU", "prompt_len": args.prompt_len, "layers": args.layers, "layers_full": FULL_LAYERS,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
+            "moe_inter": cfg.moe_intermediate_size, "shared_inter": cfg.shared_expert_intermediate_size,
+            "vocab": cfg.vocab_size, "page_size": page,
+            "l2": "inputs larger than L2: a step reads %.1f GB" % (step_bytes / 1e9),
+            "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(eng.cache.last_h2d_bytes), "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(main_run["launches"]),
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "load_s": round(load_s, 1),
+    }
+    if not args.no_points:
+        pts = {}
+        for b in (1, 64):
+            r = decode_run(b, max(8, args.steps // 2), 3)
+            pts[f"decode_b{b}"] = round(b * max(8, args.steps // 2) / (r["dev_ms"] / 1e3), 2)
+        out["points"] = pts
+        # prefill of one 2,048-token prompt as one step
+        T = 2048
+        times = []
+        for it in range(4):
+            s = eng.cache.open()
+            toks = prompts(1, T)[0]
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([(s, toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            eng.cache.close(s)
+        pms = min(times[1:])
+        flops = prefill_flops(cfg, T, args.layers)
+        out["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                          "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    eng.rt.ops.check_errors()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -60,6 +60,7 @@ class ModelCache:
             [host.GroupSpec(self.page_size, w, self.num_pages) for w in self.group_windows], self.num_slots)
         self._pinned = []
         self._ring = 0
+        self.last_h2d_bytes = 0      # size of the last step's metadata copy
 
     # ------------------------------------------------------------ requests
     def open(self) -> int:
@@ -116,6 +117,7 @@ class ModelCache:
         sitems = [host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
         lay = self.manager.plan_layout(sitems, fixed_table_width)
         stage, ent = self._staging(lay.total)
+        self.last_h2d_bytes = 4 * lay.total
         self.manager.pack(sitems, lay, stage.data_ptr(), stage.numel())
         if into is not None:
             if into.numel() < lay.total:

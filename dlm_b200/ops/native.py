@@ -40,6 +40,7 @@ class NativeOps:
             raise KernelError("dlm_b200 needs a CUDA device: there is no CPU path")
         self.k = load_kernels()
         self.fast = 1 if fast else 0
+        self.launches = 0        # kernels launched through this object (for the benchmark's count)
 
     @staticmethod
     def _stream() -> int:
@@ -57,6 +58,7 @@ class NativeOps:
     def embed(self, tokens, table):
         T, (V, H) = tokens.numel(), table.shape
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        self.launches += 1
         self.k.embed(_p(tokens), _p(table), _p(out), T, H, V, _dt(table.dtype), self._stream())
         return out
 
@@ -64,12 +66,14 @@ class NativeOps:
         H = x.shape[-1]
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, H), dtype=out_dtype, device=x.device)
+        self.launches += 1
         self.k.rmsnorm(_p(x), _p(w), _p(out), _p(rows), n, H, float(eps), _dt(out_dtype), self._stream())
         return out
 
     # -------------------------------------------------------------- products
     def _gemm(self, a, w, out, M, N, K, epilogue, *, bias=None, a_rows=None, offsets=None, num_experts=0,
               w_expert_stride=0, ldo=None):
+        self.launches += 1
         self.k.gemm(_p(a), a.stride(0), _p(a_rows), _p(w), K, w_expert_stride, _p(offsets), num_experts, _p(bias),
                     _p(out), out.stride(0) if ldo is None else ldo, M, N, K, _dt(a.dtype), _dt(out.dtype), epilogue,
                     self.fast, self._stream())
@@ -114,6 +118,7 @@ class NativeOps:
         total_pages, nkv_c, page_size, hd_c = k_cache.shape
         assert (nkv_c, hd_c) == (nkv, hd) and k_cache.dtype == out_dtype
         q = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
+        self.launches += 1
         self.k.rope_kv_write(_p(qkv), _p(positions), _p(inv_freq), int(rotary_dim), _p(slots), _p(q), _p(k_cache),
                              _p(v_cache), T, nh, nkv, hd, page_size, total_pages, _dt(out_dtype), self._stream())
         return q
@@ -124,6 +129,7 @@ class NativeOps:
         R, width = block_table.shape
         total_pages, _, page_size, _ = k_cache.shape
         out = torch.empty_like(q)
+        self.launches += 1
         self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
                          nh, nkv, hd, page_size, total_pages, int(window), float(scale), int(max_q_len),
                          int(max_kv_len), _dt(q.dtype), self.fast, self._stream())
@@ -136,6 +142,7 @@ class NativeOps:
         ids = torch.empty((T, k), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, k), dtype=torch.float32, device=h.device)
         gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
+        self.launches += 1
         self.k.router_topk(_p(h), _p(w), _p(ids), _p(wts), _p(gate), T, H, E, k, int(norm), int(has_gate),
                            _dt(h.dtype), self._stream())
         return ids, wts, gate
@@ -146,11 +153,13 @@ class NativeOps:
         offsets = torch.empty((E + 1,), dtype=torch.int32, device=ids.device)
         rows = torch.empty((n,), dtype=torch.int32, device=ids.device)
         dest = torch.empty((T, k), dtype=torch.int32, device=ids.device)
+        self.launches += 1
         self.k.moe_permute(_p(ids), n, k, E, _p(offsets), _p(rows), _p(dest), self._stream())
         return offsets, rows, dest
 
     def moe_combine(self, y, dest, wts, shared, gate, resid):
         T, H = resid.shape
+        self.launches += 1
         self.k.moe_combine(_p(y), _p(dest), _p(wts), _p(shared), _p(gate), _p(resid), T, H, dest.shape[1],
                            self._stream())
 
@@ -158,6 +167,7 @@ class NativeOps:
     def argmax(self, logits):
         N, V = logits.shape
         out = torch.empty((N,), dtype=torch.int32, device=logits.device)
+        self.launches += 1
         self.k.argmax(_p(logits), _p(out), N, V, self._stream())
         return out
 
@@ -165,6 +175,7 @@ class NativeOps:
         N, V = logits.shape
         out = torch.empty((N,), dtype=torch.int32, device=logits.device)
         scratch = torch.empty((N, V), dtype=torch.float32, device=logits.device)
+        self.launches += 1
         self.k.sample(_p(logits), _p(out), N, V, _p(params), _p(top_k), _p(u), _p(seen_offsets), _p(seen_tokens),
                       _p(scratch), self._stream())
         return out

@@ -26,7 +26,7 @@ from .safetensors_io import save_file
 _GOLDEN = 0x9E3779B97F4A7C15
 _C1 = 0xBF58476D1CE4E5B9
 _C2 = 0x94D049BB133111EB
-_CHUNK = 1 << 22
+_CHUNK = 1 << 24
 
 
 def _s64(v: int) -> int:

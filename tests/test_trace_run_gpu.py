@@ -1,0 +1,92 @@
+"""bin/trace_run as a user runs it: a child process fed steps on standard input, one at a
+time, each after the previous ``done``; its files are compared with the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import cuttings
+import plain_qwen2_moe as plain
+from tiny_configs import TINY, pick_prompt
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 1e-4, "bfloat16": 1e-2}
+MARGIN = {"float32": 1e-6, "bfloat16": 2e-4}
+
+
+def replay(folder, dtype, steps, out_dir, max_tokens):
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+           "--out", out_dir, "--max-tokens", str(max_tokens)]
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    try:
+        for st in steps:
+            proc.stdin.write(json.dumps(st) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline().strip()
+            assert line == f"done {st['step']}", f"expected 'done {st['step']}', got {line!r}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+
+
+def read_logits(out_dir, steps, vocab):
+    got, fed = {}, {}
+    for st in steps:
+        wanted = sum(len(e["want"]) for e in st["entries"])
+        path = os.path.join(out_dir, f"{st['step']}.f32")
+        if wanted == 0:
+            assert not os.path.exists(path)
+            for e in st["entries"]:
+                fed[e["id"]] = fed.get(e["id"], 0) + len(e["tokens"])
+            continue
+        arr = np.fromfile(path, dtype="<f4")
+        assert arr.size == wanted * vocab
+        arr = torch.from_numpy(arr.reshape(wanted, vocab).copy())
+        row = 0
+        for e in st["entries"]:
+            base = fed.get(e["id"], 0)
+            for w in e["want"]:
+                got[(e["id"], base + w)] = arr[row]
+                row += 1
+            fed[e["id"]] = base + len(e["tokens"])
+    return got
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_mixed(name, dtype, tiny_folders, tmp_path):
+    V = TINY[name]["cfg"]["vocab_size"]
+    oracle = plain.PlainModel(tiny_folders[name], compute=torch.float64, emulate_bf16=(dtype == "bfloat16"))
+    reqs = {f"q{i}": pick_prompt(oracle, 200 + i, n, V, MARGIN[dtype]) for i, n in enumerate([70, 33, 100, 16, 90, 5])}
+    toks = {rid: t for rid, (t, _) in reqs.items()}
+    steps, _ = cuttings.mixed(toks, max_live=4, seed=9)
+    # some entries ask for nothing, some for a part
+    for i, st in enumerate(steps):
+        if i % 5 == 1:
+            for e in st["entries"]:
+                if len(e["tokens"]) > 1:
+                    e["want"] = e["want"][-1:]
+    peak = cuttings.peak_tokens(steps)
+    out_dir = str(tmp_path / "out")
+    replay(tiny_folders[name], dtype, steps, out_dir, peak)
+    got = read_logits(out_dir, steps, V)
+    assert got, "no logits were written"
+    checked = 0
+    full = {rid: oracle.logits(t) for rid, (t, _) in reqs.items()}
+    for (rid, p), row in got.items():
+        t, clear = reqs[rid]
+        if p >= clear:
+            continue
+        ref = full[rid][p]
+        d = float((row - ref).abs().max())
+        assert d <= TOL[dtype], f"{rid} position {p}: {d:.3e}"
+        checked += 1
+    assert checked > 0.25 * len(got)
