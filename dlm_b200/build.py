@@ -104,7 +104,7 @@ def _hash(files: list[str], flags: list[str]) -> str:
         h.update(os.path.basename(f).encode())
         with open(f, "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(flags).encode())
+    h.update(" ".join(f.replace(_PKG, "<pkg>") for f in flags).encode())
     h.update(sys.version.encode())
     return h.hexdigest()[:20]
 
