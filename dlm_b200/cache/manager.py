@@ -148,7 +148,8 @@ class ModelCache:
                          positions=sl(lay.off_positions, T), token_req=sl(lay.off_token_req, T),
                          cu_q=sl(lay.off_cu_q, R + 1), kv_len=sl(lay.off_kv_len, R),
                          state_slot=sl(lay.off_state_slot, R), logit_rows=sl(lay.off_logit_rows, N),
-                         groups=groups, max_q_len=lay.max_q_len, max_kv_len=lay.max_kv_len)
+                         groups=groups, max_q_len=lay.max_q_len, max_kv_len=lay.max_kv_len,
+                         num_single=lay.num_single)
 
     def stats(self):
         return [self.manager.stats(g) for g in range(len(self.group_windows))]

@@ -42,6 +42,7 @@ PYBIND11_MODULE(_dlm_host, m) {
         .def_readonly("num_groups", &StepLayout::num_groups)
         .def_readonly("max_q_len", &StepLayout::max_q_len)
         .def_readonly("max_kv_len", &StepLayout::max_kv_len)
+        .def_readonly("num_single", &StepLayout::num_single)
         .def_readonly("table_width", &StepLayout::table_width)
         .def_readonly("off_tokens", &StepLayout::off_tokens)
         .def_readonly("off_positions", &StepLayout::off_positions)

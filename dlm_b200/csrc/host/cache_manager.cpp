@@ -188,6 +188,7 @@ StepLayout CacheManager::plan_layout(const std::vector<StepItem>& items, int min
         for (int w : it.want)
             if (w < 0 || w >= q) throw std::invalid_argument("wanted place is outside the item's tokens");
         lay.num_tokens += q;
+        if (q == 1) ++lay.num_single;
         lay.num_wanted += (int)it.want.size();
         lay.max_q_len = std::max(lay.max_q_len, q);
         lay.max_kv_len = std::max(lay.max_kv_len, kv);

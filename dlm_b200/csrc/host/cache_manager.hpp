@@ -53,6 +53,7 @@ struct StepItem {
 struct StepLayout {
     int num_tokens = 0, num_requests = 0, num_wanted = 0, num_groups = 0;
     int max_q_len = 0, max_kv_len = 0;
+    int num_single = 0;            // requests with exactly one token in this step
     std::vector<int> table_width;  // per group
     // offsets into the int32 buffer
     int off_tokens = 0, off_positions = 0, off_token_req = 0, off_cu_q = 0, off_kv_len = 0,

@@ -38,10 +38,14 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
                    int page_size, int total_pages, int dtype, cudaStream_t stream);
 
 // Causal (optionally windowed) attention of every token of the step over its request's paged keys and values.
+// num_single: how many requests have exactly one query token.  With fast != 0 and a scratch buffer of
+// attention_scratch_floats(...) floats those go to the split-key decode kernel.
 void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
                const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
-               int page_size, int total_pages, int window, float scale, int max_q_len, int max_kv_len, int dtype,
-               int fast, cudaStream_t stream);
+               int page_size, int total_pages, int window, float scale, int max_q_len, int max_kv_len,
+               int num_single, float* scratch, int dtype, int fast, cudaStream_t stream);
+// Floats of scratch the decode kernel needs for a step of R requests whose longest holds max_kv_len tokens.
+size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 
 // Router: logits = h · w^T (32-bit), softmax over E, top-k (ties: lower index), optional renormalisation.
 // has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).

@@ -1,0 +1,285 @@
+// Decode attention: one query token per request against its paged keys and values.
+// Memory-bound, so the work is cut for bandwidth: the keys of a request are split into
+// chunks, one block per (request, kv head, chunk) streams its chunk once with 16-byte
+// loads and serves every query head of the kv head's group from the same registers; the
+// chunks' partial results (maximum, sum, weighted values) are merged by a second kernel.
+// Requests with more than one query token in the step are skipped (the prefill kernel has them).
+#include "api.h"
+#include "attention_internal.h"
+#include "common.cuh"
+
+namespace dlmk {
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int UNROLL = 4;
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+template <> struct Vec8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+
+// LPK lanes share a key (each holds 8 head dims); GT query heads of the group are served together.
+template <typename T, int LPK, int GT>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                        const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ cu_q,
+                        const int32_t* __restrict__ kv_len, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int chunk,
+                        int n_splits, int head_passes, int* err) {
+    constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
+    constexpr int STREAMS = WARPS * KPW;
+    extern __shared__ float smem[];
+    float* sm_m = smem;                           // [STREAMS][GT]
+    float* sm_l = sm_m + STREAMS * GT;            // [STREAMS][GT]
+    float* sm_o = sm_l + STREAMS * GT;            // [STREAMS][GT][LPK * 8]
+
+    const int r = blockIdx.x;
+    const int kvh = blockIdx.y / head_passes, pass = blockIdx.y % head_passes;
+    const int sp = blockIdx.z;
+    if (cu_q[r + 1] - cu_q[r] != 1) return;
+    const int group = nh / nkv;
+    const int h0 = kvh * group + pass * GT;                       // first query head of this block
+    const int n_heads = min(GT, group - pass * GT);
+    const int len = kv_len[r], p = len - 1;
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int j_begin = max(lo, sp * chunk), j_end = min(len, (sp + 1) * chunk);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int li = lane % LPK, ks = lane / LPK;
+    const int d0 = li * 8;
+    const bool dim_ok = d0 < hd;                                   // hd is a multiple of 8
+    const int token = cu_q[r];
+
+    float qv[GT][8];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qv[g][i] = 0.f;
+        if (g < n_heads && dim_ok) Vec8<T>::load(q + (long long)token * nh * hd + (h0 + g) * hd + d0, qv[g]);
+    }
+    float m[GT], l[GT], acc[GT][8];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+    }
+
+    const int32_t* table = block_table + (long long)r * table_width;
+    const int stride = STREAMS;                                    // keys per block iteration
+    // The trip count is the same for every lane of a warp (the shuffles below name all 32 lanes):
+    // the loop runs over the warp's first key, each lane adds its own key slot.
+    for (int jw = j_begin + warp * KPW; jw < j_end; jw += stride * UNROLL) {
+        float kf[UNROLL][8], vf[UNROLL][8];
+        bool ok[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = jw + ks + u * stride;
+            ok[u] = j < j_end;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
+            if (ok[u]) {
+                const int lp = j / page_size;
+                const int page = lp < table_width ? table[lp] : -1;
+                if (page >= 0 && page < total_pages) {
+                    if (dim_ok) {
+                        const long long off = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * hd + d0;
+                        Vec8<T>::load(k_cache + off, kf[u]);
+                        Vec8<T>::load(v_cache + off, vf[u]);
+                    }
+                } else {
+                    *err = 3;
+                    ok[u] = false;
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            if (g >= n_heads) break;
+            float s[UNROLL];
+            float mx = m[g];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                float d = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kf[u][i], d);
+#pragma unroll
+                for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                s[u] = ok[u] ? d * scale : -INFINITY;
+                mx = fmaxf(mx, s[u]);
+            }
+            if (mx == -INFINITY) continue;
+            const float alpha = expf(m[g] - mx);
+            float lsum = l[g] * alpha;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] *= alpha;
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const float pu = ok[u] ? expf(s[u] - mx) : 0.f;
+                lsum += pu;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(pu, vf[u][i], acc[g][i]);
+            }
+            l[g] = lsum;
+            m[g] = mx;
+        }
+    }
+
+    // merge the block's streams (fixed order)
+    const int stream = warp * KPW + ks;
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        if (li == 0) { sm_m[stream * GT + g] = m[g]; sm_l[stream * GT + g] = l[g]; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sm_o[(stream * GT + g) * (LPK * 8) + d0 + i] = acc[g][i];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_heads * hd; idx += blockDim.x) {
+        const int g = idx / hd, d = idx % hd;
+        float mx = -INFINITY;
+        for (int s2 = 0; s2 < STREAMS; ++s2) mx = fmaxf(mx, sm_m[s2 * GT + g]);
+        float o = 0.f, ls = 0.f;
+        if (mx != -INFINITY) {
+            for (int s2 = 0; s2 < STREAMS; ++s2) {
+                const float ms = sm_m[s2 * GT + g];
+                if (ms == -INFINITY) continue;
+                const float a = expf(ms - mx);
+                o = fmaf(a, sm_o[(s2 * GT + g) * (LPK * 8) + d], o);
+                ls = fmaf(a, sm_l[s2 * GT + g], ls);
+            }
+        }
+        const long long base = ((long long)r * nh + (h0 + g)) * n_splits + sp;
+        part_o[base * hd + d] = o;
+        if (d == 0) { part_ml[base * 2] = mx; part_ml[base * 2 + 1] = ls; }
+    }
+}
+
+template <typename T>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int32_t* __restrict__ cu_q, T* __restrict__ out, int nh, int hd,
+                                              int n_splits) {
+    const int r = blockIdx.x, h = blockIdx.y;
+    if (cu_q[r + 1] - cu_q[r] != 1) return;
+    const long long base = ((long long)r * nh + h) * n_splits;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
+    T* o = out + (long long)cu_q[r] * nh * hd + h * hd;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float acc = 0.f, ls = 0.f;
+        if (mx != -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const float ms = part_ml[(base + s) * 2];
+                if (ms == -INFINITY) continue;
+                const float a = expf(ms - mx);
+                acc = fmaf(a, part_o[(base + s) * hd + d], acc);
+                ls = fmaf(a, part_ml[(base + s) * 2 + 1], ls);
+            }
+        }
+        o[d] = from_f32<T>(ls > 0.f ? acc / ls : 0.f);
+    }
+}
+
+template <typename T, int LPK>
+void launch_decode(int gt, dim3 grid, size_t smem_bytes, cudaStream_t stream, const void* q, const void* k_cache,
+                   const void* v_cache, const int32_t* block_table, int table_width, const int32_t* cu_q,
+                   const int32_t* kv_len, float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
+                   int total_pages, int window, float scale, int chunk, int n_splits, int head_passes, int* err) {
+#define DLM_LAUNCH(GT)                                                                                         \
+    attention_decode_kernel<T, LPK, GT><<<grid, WARPS * 32, smem_bytes, stream>>>(                             \
+        static_cast<const T*>(q), static_cast<const T*>(k_cache), static_cast<const T*>(v_cache), block_table, \
+        table_width, cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk, \
+        n_splits, head_passes, err)
+    if (gt == 1) DLM_LAUNCH(1);
+    else if (gt == 2) DLM_LAUNCH(2);
+    else if (gt == 4) DLM_LAUNCH(4);
+    else DLM_LAUNCH(8);
+#undef DLM_LAUNCH
+}
+
+}  // namespace
+
+bool attention_decode_ok(int hd) { return hd % 8 == 0 && hd >= 8 && hd <= 256; }
+
+void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk) {
+    // enough blocks to keep every SM streaming, chunks of at least 64 keys
+    int splits = (592 + R * nkv - 1) / (R * nkv);
+    const int max_splits = (max_kv_len + 63) / 64;
+    splits = splits < 1 ? 1 : (splits > max_splits ? max_splits : splits);
+    if (splits > 64) splits = 64;
+    int c = (max_kv_len + splits - 1) / splits;
+    c = (c + 63) / 64 * 64;
+    *chunk = c;
+    *n_splits = (max_kv_len + c - 1) / c;
+}
+
+size_t attention_decode_scratch_floats(int R, int nh, int hd, int n_splits) {
+    return (size_t)R * nh * n_splits * (hd + 2);
+}
+
+void attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                      int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch, int R,
+                      int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int n_splits,
+                      int chunk, int dtype, cudaStream_t stream) {
+    if (R <= 0) return;
+    DLM_CHECK(attention_decode_ok(hd), "decode attention: head_dim must be a multiple of 8, at most 256");
+    DLM_CHECK(nh % nkv == 0, "attention: heads must be a multiple of kv heads");
+    const int group = nh / nkv;
+    const int gt = group >= 8 ? 8 : (group > 2 ? (group > 4 ? 8 : 4) : group);
+    const int head_passes = (group + gt - 1) / gt;
+    int lpk = 1;
+    while (lpk * 8 < hd) lpk <<= 1;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)R * nh * n_splits * hd;
+    dim3 grid(R, nkv * head_passes, n_splits);
+    int* err = error_flag_ptr();
+    const int streams = WARPS * (32 / lpk);
+    const size_t smem_bytes = sizeof(float) * ((size_t)streams * gt * 2 + (size_t)streams * gt * lpk * 8);
+#define DLM_DISPATCH(T)                                                                                            \
+    switch (lpk) {                                                                                                 \
+        case 1: launch_decode<T, 1>(gt, grid, smem_bytes, stream, q, k_cache, v_cache, block_table, table_width,   \
+                    cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,      \
+                    n_splits, head_passes, err); break;                                                            \
+        case 2: launch_decode<T, 2>(gt, grid, smem_bytes, stream, q, k_cache, v_cache, block_table, table_width,   \
+                    cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,      \
+                    n_splits, head_passes, err); break;                                                            \
+        case 4: launch_decode<T, 4>(gt, grid, smem_bytes, stream, q, k_cache, v_cache, block_table, table_width,   \
+                    cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,      \
+                    n_splits, head_passes, err); break;                                                            \
+        case 8: launch_decode<T, 8>(gt, grid, smem_bytes, stream, q, k_cache, v_cache, block_table, table_width,   \
+                    cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,      \
+                    n_splits, head_passes, err); break;                                                            \
+        case 16: launch_decode<T, 16>(gt, grid, smem_bytes, stream, q, k_cache, v_cache, block_table, table_width, \
+                    cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,      \
+                    n_splits, head_passes, err); break;                                                            \
+        default: launch_decode<T, 32>(gt, grid, smem_bytes, stream, q, k_cache, v_cache, block_table, table_width, \
+                    cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,      \
+                    n_splits, head_passes, err); break;                                                            \
+    }
+    if (dtype == F32) { DLM_DISPATCH(float) } else { DLM_DISPATCH(__nv_bfloat16) }
+#undef DLM_DISPATCH
+    check_launch("attention_decode");
+    dim3 mgrid(R, nh);
+    if (dtype == F32)
+        attention_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
+    else
+        attention_decode_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
+    check_launch("attention_decode_merge");
+}
+
+}  // namespace dlmk

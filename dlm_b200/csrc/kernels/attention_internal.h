@@ -1,0 +1,26 @@
+// Kernels behind dlmk::attention (see api.h for the meaning of the arguments).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace dlmk {
+
+// FMA-unit kernel for any mix of query lengths.  skip_single != 0: requests with exactly one query token are
+// left to the decode kernel.
+void attention_simt(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                    int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
+                    int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                    int dtype, cudaStream_t stream);
+
+// Split-key decode kernel for requests with exactly one query token (bfloat16 and float32).
+bool attention_decode_ok(int hd);
+void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk);
+size_t attention_decode_scratch_floats(int R, int nh, int hd, int n_splits);
+void attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                      int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch, int R,
+                      int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int n_splits,
+                      int chunk, int dtype, cudaStream_t stream);
+
+}  // namespace dlmk

@@ -7,6 +7,7 @@
 // query's result does not depend on how its request was cut into steps, on the other
 // requests of the batch, or on which pages hold its keys.
 #include "api.h"
+#include "attention_internal.h"
 #include "common.cuh"
 
 namespace dlmk {
@@ -25,7 +26,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ cu_q,
                       const int32_t* __restrict__ kv_len, T* __restrict__ out, int R, int nh, int nkv, int hd,
-                      int page_size, int total_pages, int window, float scale, int* err) {
+                      int page_size, int total_pages, int window, float scale, int skip_single, int* err) {
     extern __shared__ float smem[];
     float* Qs = smem;                               // [BQ][hd]
     float* Ks = Qs + BQ * hd;                       // [BKV][hd + 1]
@@ -43,7 +44,7 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
         s_map[0] = -1;
         for (int r = 0; r < R; ++r) {
             const int ql = cu_q[r + 1] - cu_q[r];
-            const int tiles = (ql + BQ - 1) / BQ;
+            const int tiles = (skip_single && ql == 1) ? 0 : (ql + BQ - 1) / BQ;
             if ((int)blockIdx.x < acc + tiles) {
                 s_map[0] = r;
                 s_map[1] = ((int)blockIdx.x - acc) * BQ;
@@ -158,8 +159,8 @@ attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, co
 
 void attention_simt(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                     int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
-                    int nkv, int hd, int page_size, int total_pages, int window, float scale, int dtype,
-                    cudaStream_t stream) {
+                    int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                    int dtype, cudaStream_t stream) {
     if (T <= 0 || R <= 0) return;
     DLM_CHECK(hd > 0 && hd <= MAX_HD, "attention: head_dim must be in 1..256");
     DLM_CHECK(nh % nkv == 0, "attention: heads must be a multiple of kv heads");
@@ -172,25 +173,16 @@ void attention_simt(const void* q, const void* k_cache, const void* v_cache, con
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kern<<<grid, WARPS * 32, smem, stream>>>(static_cast<const float*>(q), static_cast<const float*>(k_cache),
             static_cast<const float*>(v_cache), block_table, table_width, cu_q, kv_len, static_cast<float*>(out), R,
-            nh, nkv, hd, page_size, total_pages, window, scale, err);
+            nh, nkv, hd, page_size, total_pages, window, scale, skip_single, err);
     } else {
         auto kern = attention_simt_kernel<__nv_bfloat16>;
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kern<<<grid, WARPS * 32, smem, stream>>>(static_cast<const __nv_bfloat16*>(q),
             static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), block_table,
             table_width, cu_q, kv_len, static_cast<__nv_bfloat16*>(out), R, nh, nkv, hd, page_size, total_pages,
-            window, scale, err);
+            window, scale, skip_single, err);
     }
     check_launch("attention_simt");
-}
-
-void attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table, int table_width,
-               const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh, int nkv, int hd,
-               int page_size, int total_pages, int window, float scale, int max_q_len, int max_kv_len, int dtype,
-               int fast, cudaStream_t stream) {
-    (void)fast; (void)max_q_len; (void)max_kv_len;
-    attention_simt(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd, page_size,
-                   total_pages, window, scale, dtype, stream);
 }
 
 }  // namespace dlmk

@@ -41,11 +41,15 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("attention", [](u64 q, u64 k_cache, u64 v_cache, u64 block_table, int table_width, u64 cu_q, u64 kv_len,
                           u64 out, int T, int R, int nh, int nkv, int hd, int page_size, int total_pages, int window,
-                          float scale, int max_q_len, int max_kv_len, int dtype, int fast, u64 stream) {
+                          float scale, int max_q_len, int max_kv_len, int num_single, u64 scratch, int dtype, int fast,
+                          u64 stream) {
         dlmk::attention(ptr<const void>(q), ptr<const void>(k_cache), ptr<const void>(v_cache),
                         ptr<const int32_t>(block_table), table_width, ptr<const int32_t>(cu_q),
                         ptr<const int32_t>(kv_len), ptr<void>(out), T, R, nh, nkv, hd, page_size, total_pages, window,
-                        scale, max_q_len, max_kv_len, dtype, fast, st(stream));
+                        scale, max_q_len, max_kv_len, num_single, ptr<float>(scratch), dtype, fast, st(stream));
+    });
+    m.def("attention_scratch_floats", [](int R, int nh, int nkv, int hd, int max_kv_len) {
+        return dlmk::attention_scratch_floats(R, nh, nkv, hd, max_kv_len);
     });
     m.def("router_topk", [](u64 h, u64 w, u64 ids, u64 wts, u64 gate, int T, int H, int E, int k, int norm,
                             int has_gate, int dtype, u64 stream) {

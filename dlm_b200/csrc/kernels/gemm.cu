@@ -8,7 +8,21 @@ namespace dlmk {
 void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
           const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N, int K,
           int in_dtype, int out_dtype, int epilogue, int fast, cudaStream_t stream) {
-    (void)fast;
+    if (fast && gemm_smallm_ok(a, lda, w, ldw, w_expert_stride, M, N, K, in_dtype)) {
+        if (expert_offsets == nullptr) {
+            if (M <= 64) {
+                gemm_smallm(a, lda, a_rows, w, ldw, w_expert_stride, nullptr, 0, bias, out, ldo, M, N, K, out_dtype,
+                            epilogue, M, stream);
+                return;
+            }
+        } else if (bias == nullptr && (long long)M <= 16LL * num_experts) {
+            // few rows per expert on average: stream each active expert's weights once
+            const int avg2 = (2 * M + num_experts - 1) / num_experts;     // twice the mean rows per expert
+            gemm_smallm(a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, nullptr, out, ldo, M, N,
+                        K, out_dtype, epilogue, avg2 <= 4 ? 8 : (avg2 <= 16 ? 16 : 32), stream);
+            return;
+        }
+    }
     gemm_simt(a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, bias, out, ldo, M, N, K, in_dtype,
               out_dtype, epilogue, stream);
 }

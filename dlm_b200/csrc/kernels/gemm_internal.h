@@ -11,4 +11,12 @@ void gemm_simt(const void* a, int lda, const int32_t* a_rows, const void* w, int
                const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
                int K, int in_dtype, int out_dtype, int epilogue, cudaStream_t stream);
 
+// Weight-streaming tensor-core kernel for few rows of A (bfloat16 inputs only).  rows_per_pass: how many
+// rows of A (of one group) meet the weights in one pass over them: up to 8, 16 or 32.
+bool gemm_smallm_ok(const void* a, int lda, const void* w, int ldw, long long w_expert_stride, int M, int N, int K,
+                    int in_dtype);
+void gemm_smallm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
+                 const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
+                 int K, int out_dtype, int epilogue, int rows_per_pass, cudaStream_t stream);
+
 }  // namespace dlmk

@@ -124,15 +124,20 @@ class NativeOps:
         return q
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len):
+                  max_kv_len, num_single=0):
         T = q.shape[0]
         R, width = block_table.shape
         total_pages, _, page_size, _ = k_cache.shape
         out = torch.empty_like(q)
-        self.launches += 1
+        scratch = None
+        if self.fast and num_single > 0:
+            n = self.k.attention_scratch_floats(R, nh, nkv, hd, int(max_kv_len))
+            if n > 0:
+                scratch = torch.empty((n,), dtype=torch.float32, device=q.device)
+        self.launches += 1 if scratch is None else (2 if num_single == R else 3)
         self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
                          nh, nkv, hd, page_size, total_pages, int(window), float(scale), int(max_q_len),
-                         int(max_kv_len), _dt(q.dtype), self.fast, self._stream())
+                         int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast, self._stream())
         return out
 
     # ------------------------------------------------------------------- moe

@@ -73,7 +73,7 @@ class GroupedQueryAttention(Mixer):
                               view.k, view.v, self.nh, self.nkv, self.hd, rt.dtype)
         o = ops.attention(q, view.k, view.v, view.group.block_table, b.cu_q, b.kv_len,
                           self.window or 0, self.scale, self.nh, self.nkv, self.hd,
-                          b.max_q_len, b.max_kv_len)
+                          b.max_q_len, b.max_kv_len, b.num_single)
         ops.linear_add(o, self.w_o, resid)
 
 

@@ -143,6 +143,7 @@ class StepBatch:
     groups: list[GroupView]
     max_q_len: int
     max_kv_len: int
+    num_single: int = 0         # requests with exactly one token in this step
 
 
 @dataclass

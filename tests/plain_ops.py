@@ -92,7 +92,7 @@ class PlainOps:
         return q.reshape(T, Q).to(out_dtype)
 
     def attention(self, q, k_cache, v_cache, block_table, cu_q, kv_len, window, scale, nh, nkv, hd, max_q_len,
-                  max_kv_len):
+                  max_kv_len, num_single=0):
         T = q.shape[0]
         ps = k_cache.shape[2]
         out = torch.zeros((T, nh * hd), dtype=torch.float32, device=q.device)

@@ -70,7 +70,8 @@ def test_rmsnorm_hand_value(ops):
 
 
 # ------------------------------------------------------------------------ products
-GEMM_SHAPES = [(1, 64, 64), (5, 97, 130), (64, 128, 256), (130, 200, 72), (257, 330, 1000), (3, 1408, 2048)]
+GEMM_SHAPES = [(1, 64, 64), (5, 97, 130), (64, 128, 256), (130, 200, 72), (257, 330, 1000), (3, 1408, 2048),
+               (8, 2048, 1408), (16, 100, 72), (33, 200, 200), (2, 48, 40), (9, 2816, 2048), (1, 300, 5632)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -97,7 +98,7 @@ def test_linear_add_and_swiglu(ops, ref, dtype, M, N, K):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("E,k,T,H,I", [(5, 1, 9, 72, 40), (8, 2, 33, 64, 32), (12, 3, 130, 256, 48),
-                                       (60, 4, 7, 512, 176)])
+                                       (60, 4, 7, 512, 176), (12, 3, 20, 256, 48), (60, 4, 64, 2048, 1408)])
 def test_grouped_products(ops, ref, dtype, E, k, T, H, I):
     h = rand((T, H), dtype, 9)
     g = torch.Generator().manual_seed(E)
@@ -248,7 +249,8 @@ def test_attention(ops, slow_ops, ref, dtype, nh, nkv, hd, ps, window, reqs, fas
     q = rand((T, nh * hd), dtype, 22)
     scale = 1 / math.sqrt(hd)
     mq, mk = max(q for _, q in reqs), max(n for n, _ in reqs)
-    got = o.attention(q, k, v, table, cu_q, kv_len, window, scale, nh, nkv, hd, mq, mk)
+    ns = sum(1 for _, ql in reqs if ql == 1)
+    got = o.attention(q, k, v, table, cu_q, kv_len, window, scale, nh, nkv, hd, mq, mk, ns)
     want = ref.attention(q, k, v, table, cu_q, kv_len, window, scale, nh, nkv, hd, mq, mk)
     close(got, want, **(dict(rtol=1e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-2)))
     o.check_errors()
@@ -271,7 +273,7 @@ def test_attention_far_key_stands_out(ops, slow_ops, dtype, fast, far):
     for h in range(nh):
         g = h // (nh // nkv)
         q[0, h * hd:(h + 1) * hd] = q[0, (g * (nh // nkv)) * hd:(g * (nh // nkv) + 1) * hd]
-    got = o.attention(q, k, v, table, cu_q, kv_len, 0, 1 / math.sqrt(hd), nh, nkv, hd, 1, n).float().view(nh, hd)
+    got = o.attention(q, k, v, table, cu_q, kv_len, 0, 1 / math.sqrt(hd), nh, nkv, hd, 1, n, 1).float().view(nh, hd)
     for h in range(nh):
         close(got[h], v[page, h // (nh // nkv), off].float(), rtol=2e-2, atol=2e-2)
 
@@ -288,7 +290,7 @@ def test_attention_window_edge(ops, slow_ops, fast):
     p = n - 1
     for j, boost in ((p - W + 1, 30.0), (p - W, 60.0)):
         k[j // ps, 0, j % ps] = q[0] * boost
-    got = o.attention(q, k, v, table, cu_q, kv_len, W, 1 / math.sqrt(hd), nh, nkv, hd, 1, n)
+    got = o.attention(q, k, v, table, cu_q, kv_len, W, 1 / math.sqrt(hd), nh, nkv, hd, 1, n, 1)
     inside = p - W + 1
     close(got[0], v[inside // ps, 0, inside % ps], rtol=1e-3, atol=1e-3)
 
