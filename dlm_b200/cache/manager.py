@@ -132,6 +132,22 @@ class ModelCache:
             ent[1] = ev
         return self.batch_from_layout(lay, dev)
 
+    def fill_metadata(self, sitems, lay, dev: torch.Tensor) -> None:
+        """Packs a step's metadata with a layout fixed earlier and copies it into ``dev`` (a device
+        buffer that a captured graph reads).  The items must give the same layout sizes."""
+        now = self.manager.plan_layout(sitems, lay.table_width[0] if lay.table_width else 0)
+        if (now.total, now.num_tokens, now.num_requests, now.num_wanted) != \
+                (lay.total, lay.num_tokens, lay.num_requests, lay.num_wanted):
+            raise ValueError("the step does not fit the fixed metadata layout")
+        stage, ent = self._staging(lay.total)
+        self.last_h2d_bytes = 4 * lay.total
+        self.manager.pack(sitems, lay, stage.data_ptr(), stage.numel())
+        dev[:lay.total].copy_(stage[:lay.total], non_blocking=True)
+        if ent is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            ent[1] = ev
+
     def batch_from_layout(self, lay, dev: torch.Tensor) -> StepBatch:
         T, R, N = lay.num_tokens, lay.num_requests, lay.num_wanted
 

@@ -61,8 +61,10 @@ void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int3
 void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
                  float* resid, int T, int H, int k, cudaStream_t stream);
 
-// out[i] = index of the first maximum of logits[i, :]
-void argmax(const float* logits, int32_t* out, int N, int V, cudaStream_t stream);
+// out[i] = index of the first maximum of logits[i, :].  scratch: argmax_scratch_bytes(N, V) bytes (may be
+// nullptr when that is 0; a large vocabulary is then searched by one block per row).
+void argmax(const float* logits, int32_t* out, int N, int V, void* scratch, cudaStream_t stream);
+size_t argmax_scratch_bytes(int N, int V);
 
 // Per row: repetition penalty over seen tokens, then greedy (temperature <= 0) or temperature / top-k / top-p /
 // min-p sampling with the uniform number u[i] (candidates ordered by logit descending, ties by index).

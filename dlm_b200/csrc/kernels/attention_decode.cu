@@ -34,20 +34,35 @@ template <> struct Vec8<float> {
     }
 };
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // LPK lanes share a key (each holds 8 head dims); GT query heads of the group are served together.
+// Keys and values arrive in shared memory in tiles of `tile` keys, two tiles in flight
+// (asynchronous 16-byte copies), so that the loads of the next tile overlap the arithmetic of this one.
 template <typename T, int LPK, int GT>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                         const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ cu_q,
                         const int32_t* __restrict__ kv_len, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int chunk,
-                        int n_splits, int head_passes, int* err) {
+                        int n_splits, int head_passes, int tile, int max_pages, int* err) {
     constexpr int KPW = 32 / LPK;                 // keys per warp per iteration
     constexpr int STREAMS = WARPS * KPW;
-    extern __shared__ float smem[];
-    float* sm_m = smem;                           // [STREAMS][GT]
-    float* sm_l = sm_m + STREAMS * GT;            // [STREAMS][GT]
-    float* sm_o = sm_l + STREAMS * GT;            // [STREAMS][GT][LPK * 8]
+    constexpr int EPC = 16 / (int)sizeof(T);      // elements per 16-byte chunk
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* Ks = reinterpret_cast<T*>(smem_raw);                       // [2][tile][hd]
+    T* Vs = Ks + 2 * tile * hd;                                   // [2][tile][hd]
+    float* sm_m = reinterpret_cast<float*>(Vs + 2 * tile * hd);   // [STREAMS][GT]
+    float* sm_l = sm_m + STREAMS * GT;                            // [STREAMS][GT]
+    float* sm_o = sm_l + STREAMS * GT;                            // [STREAMS][GT][LPK * 8]
+    int* s_table = reinterpret_cast<int*>(sm_o + STREAMS * GT * LPK * 8);   // [max_pages]
 
     const int r = blockIdx.x;
     const int kvh = blockIdx.y / head_passes, pass = blockIdx.y % head_passes;
@@ -60,19 +75,12 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int j_begin = max(lo, sp * chunk), j_end = min(len, (sp + 1) * chunk);
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int li = lane % LPK, ks = lane / LPK;
     const int d0 = li * 8;
     const bool dim_ok = d0 < hd;                                   // hd is a multiple of 8
     const int token = cu_q[r];
 
-    float qv[GT][8];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qv[g][i] = 0.f;
-        if (g < n_heads && dim_ok) Vec8<T>::load(q + (long long)token * nh * hd + (h0 + g) * hd + d0, qv[g]);
-    }
     float m[GT], l[GT], acc[GT][8];
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
@@ -81,63 +89,110 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
         for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
     }
 
-    const int32_t* table = block_table + (long long)r * table_width;
-    const int stride = STREAMS;                                    // keys per block iteration
-    // The trip count is the same for every lane of a warp (the shuffles below name all 32 lanes):
-    // the loop runs over the warp's first key, each lane adds its own key slot.
-    for (int jw = j_begin + warp * KPW; jw < j_end; jw += stride * UNROLL) {
-        float kf[UNROLL][8], vf[UNROLL][8];
-        bool ok[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int j = jw + ks + u * stride;
-            ok[u] = j < j_end;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
-            if (ok[u]) {
-                const int lp = j / page_size;
-                const int page = lp < table_width ? table[lp] : -1;
-                if (page >= 0 && page < total_pages) {
-                    if (dim_ok) {
-                        const long long off = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * hd + d0;
-                        Vec8<T>::load(k_cache + off, kf[u]);
-                        Vec8<T>::load(v_cache + off, vf[u]);
-                    }
-                } else {
-                    *err = 3;
-                    ok[u] = false;
-                }
-            }
-        }
+    if (j_begin < j_end) {
+        float qv[GT][8];
 #pragma unroll
         for (int g = 0; g < GT; ++g) {
-            if (g >= n_heads) break;
-            float s[UNROLL];
-            float mx = m[g];
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                float d = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kf[u][i], d);
-#pragma unroll
-                for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                s[u] = ok[u] ? d * scale : -INFINITY;
-                mx = fmaxf(mx, s[u]);
+            for (int i = 0; i < 8; ++i) qv[g][i] = 0.f;
+            if (g < n_heads && dim_ok) Vec8<T>::load(q + (long long)token * nh * hd + (h0 + g) * hd + d0, qv[g]);
+        }
+        // the pages this block touches
+        const int first_page = j_begin / page_size, last_page = (j_end - 1) / page_size;
+        const int32_t* table = block_table + (long long)r * table_width;
+        for (int i = tid; i <= last_page - first_page && i < max_pages; i += blockDim.x) {
+            const int lp = first_page + i;
+            int page = lp < table_width ? table[lp] : -1;
+            if (page < 0 || page >= total_pages) { *err = 3; page = -1; }
+            s_table[i] = page;
+        }
+        __syncthreads();
+
+        const int cpr = hd / EPC;                                  // 16-byte chunks per key row
+        auto fill = [&](int stage, int j0) {
+            T* kd = Ks + (size_t)stage * tile * hd;
+            T* vd = Vs + (size_t)stage * tile * hd;
+            for (int idx = tid; idx < tile * cpr; idx += WARPS * 32) {
+                const int key = idx / cpr, c = idx % cpr;
+                const int j = j0 + key;
+                int page = -1;
+                if (j >= j_begin && j < j_end) page = s_table[j / page_size - first_page];
+                if (page >= 0) {
+                    const long long off = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * hd + c * EPC;
+                    cp_async16(kd + key * hd + c * EPC, k_cache + off);
+                    cp_async16(vd + key * hd + c * EPC, v_cache + off);
+                } else {                                           // nothing to see: zeros, so that 0 * v stays 0
+                    *reinterpret_cast<uint4*>(kd + key * hd + c * EPC) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vd + key * hd + c * EPC) = make_uint4(0, 0, 0, 0);
+                }
             }
-            if (mx == -INFINITY) continue;
-            const float alpha = expf(m[g] - mx);
-            float lsum = l[g] * alpha;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][i] *= alpha;
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const float pu = ok[u] ? expf(s[u] - mx) : 0.f;
-                lsum += pu;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(pu, vf[u][i], acc[g][i]);
+            cp_async_commit();
+        };
+
+        const int t_begin = (j_begin / tile) * tile;
+        const int n_tiles = (j_end - t_begin + tile - 1) / tile;
+        fill(0, t_begin);
+        for (int it = 0; it < n_tiles; ++it) {
+            const int stage = it & 1;
+            const int j0 = t_begin + it * tile;
+            if (it + 1 < n_tiles) {
+                fill(stage ^ 1, j0 + tile);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
             }
-            l[g] = lsum;
-            m[g] = mx;
+            __syncthreads();
+            const T* kt = Ks + (size_t)stage * tile * hd;
+            const T* vt = Vs + (size_t)stage * tile * hd;
+            // every lane of a warp runs the same number of rounds (the shuffles name all 32 lanes)
+            for (int kb = warp * KPW; kb < tile; kb += STREAMS * UNROLL) {
+                float kf[UNROLL][8], vf[UNROLL][8];
+                bool ok[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int key = kb + ks + u * STREAMS;
+                    const int j = j0 + key;
+                    ok[u] = key < tile && j >= j_begin && j < j_end;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
+                    if (ok[u] && dim_ok) {
+                        Vec8<T>::load(kt + key * hd + d0, kf[u]);
+                        Vec8<T>::load(vt + key * hd + d0, vf[u]);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < GT; ++g) {
+                    if (g >= n_heads) break;
+                    float s[UNROLL];
+                    float mx = m[g];
+#pragma unroll
+                    for (int u = 0; u < UNROLL; ++u) {
+                        float d = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) d = fmaf(qv[g][i], kf[u][i], d);
+#pragma unroll
+                        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                        s[u] = ok[u] ? d * scale : -INFINITY;
+                        mx = fmaxf(mx, s[u]);
+                    }
+                    if (mx != -INFINITY) {
+                        const float alpha = expf(m[g] - mx);
+                        float lsum = l[g] * alpha;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[g][i] *= alpha;
+#pragma unroll
+                        for (int u = 0; u < UNROLL; ++u) {
+                            const float pu = ok[u] ? expf(s[u] - mx) : 0.f;
+                            lsum += pu;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(pu, vf[u][i], acc[g][i]);
+                        }
+                        l[g] = lsum;
+                        m[g] = mx;
+                    }
+                }
+            }
+            __syncthreads();                                      // the stage may be refilled now
         }
     }
 
@@ -200,21 +255,33 @@ void launch_decode(int gt, dim3 grid, size_t smem_bytes, cudaStream_t stream, co
                    const void* v_cache, const int32_t* block_table, int table_width, const int32_t* cu_q,
                    const int32_t* kv_len, float* part_o, float* part_ml, int nh, int nkv, int hd, int page_size,
                    int total_pages, int window, float scale, int chunk, int n_splits, int head_passes, int* err) {
+    // a tile of keys is about 16 KB per stage and tensor, and a multiple of the keys a block handles per round
+    const int streams = WARPS * (32 / LPK);
+    int tile = 16384 / (hd * (int)sizeof(T));
+    tile = tile > 64 ? 64 : tile;
+    tile = tile < streams ? streams : tile / streams * streams;
+    const int max_pages = chunk / page_size + 2;
+    smem_bytes = (size_t)4 * tile * hd * sizeof(T) + sizeof(float) * ((size_t)streams * gt * 2 +
+                 (size_t)streams * gt * LPK * 8) + sizeof(int) * max_pages;
 #define DLM_LAUNCH(GT)                                                                                         \
-    attention_decode_kernel<T, LPK, GT><<<grid, WARPS * 32, smem_bytes, stream>>>(                             \
-        static_cast<const T*>(q), static_cast<const T*>(k_cache), static_cast<const T*>(v_cache), block_table, \
-        table_width, cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk, \
-        n_splits, head_passes, err)
-    if (gt == 1) DLM_LAUNCH(1);
-    else if (gt == 2) DLM_LAUNCH(2);
-    else if (gt == 4) DLM_LAUNCH(4);
-    else DLM_LAUNCH(8);
+    {                                                                                                          \
+        auto kern = attention_decode_kernel<T, LPK, GT>;                                                       \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);              \
+        kern<<<grid, WARPS * 32, smem_bytes, stream>>>(                                                        \
+            static_cast<const T*>(q), static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),          \
+            block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages,      \
+            window, scale, chunk, n_splits, head_passes, tile, max_pages, err);                                \
+    }
+    if (gt == 1) DLM_LAUNCH(1)
+    else if (gt == 2) DLM_LAUNCH(2)
+    else if (gt == 4) DLM_LAUNCH(4)
+    else DLM_LAUNCH(8)
 #undef DLM_LAUNCH
 }
 
 }  // namespace
 
-bool attention_decode_ok(int hd) { return hd % 8 == 0 && hd >= 8 && hd <= 256; }
+bool attention_decode_ok(int hd) { return hd % 8 == 0 && hd >= 16 && hd <= 256; }
 
 void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk) {
     // enough blocks to keep every SM streaming, chunks of at least 64 keys

@@ -65,9 +65,10 @@ PYBIND11_MODULE(_dlm_kernels, m) {
         dlmk::moe_combine(ptr<const float>(y), ptr<const int32_t>(dest), ptr<const float>(wts),
                           ptr<const float>(shared), ptr<const float>(gate), ptr<float>(resid), T, H, k, st(stream));
     });
-    m.def("argmax", [](u64 logits, u64 out, int N, int V, u64 stream) {
-        dlmk::argmax(ptr<const float>(logits), ptr<int32_t>(out), N, V, st(stream));
+    m.def("argmax", [](u64 logits, u64 out, int N, int V, u64 scratch, u64 stream) {
+        dlmk::argmax(ptr<const float>(logits), ptr<int32_t>(out), N, V, ptr<void>(scratch), st(stream));
     });
+    m.def("argmax_scratch_bytes", [](int N, int V) { return dlmk::argmax_scratch_bytes(N, V); });
     m.def("sample", [](u64 logits, u64 out, int N, int V, u64 params, u64 top_k, u64 u, u64 seen_offsets,
                        u64 seen_tokens, u64 scratch, u64 stream) {
         dlmk::sample(ptr<const float>(logits), ptr<int32_t>(out), N, V, ptr<const float>(params),

@@ -66,7 +66,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 }
 
 // ------------------------------------------------------- rotary + cache write
-// One block per token; threads run over (head, pair) of q, then k, then v elements.
+// blockIdx.x = token, blockIdx.y = slice of the token's work; threads run over (head, dim) of q and k heads,
+// then over the v elements.
 template <typename T>
 __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
                                      const float* __restrict__ inv_freq, int rotary_dim,
@@ -93,7 +94,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
     }
     // q heads and k heads: rotate
     const int rot_heads = nh + nkv;
-    for (int idx = threadIdx.x; idx < rot_heads * hd; idx += blockDim.x) {
+    const int tpt = blockDim.x * gridDim.y, tid0 = blockIdx.y * blockDim.x + threadIdx.x;
+    for (int idx = tid0; idx < rot_heads * hd; idx += tpt) {
         const int h = idx / hd, d = idx % hd;
         const float* src = row + (long long)h * hd;    // q heads then k heads are contiguous in qkv
         float val;
@@ -116,7 +118,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
     }
     if (page >= 0) {
         const float* vsrc = row + Q + KV;
-        for (int idx = threadIdx.x; idx < KV; idx += blockDim.x) {
+        for (int idx = tid0; idx < KV; idx += tpt) {
             const int kh = idx / hd, d = idx % hd;
             v_cache[(((long long)page * nkv + kh) * page_size + in_page) * hd + d] = from_f32<T>(vsrc[idx]);
         }
@@ -130,7 +132,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* _
                                    const float* __restrict__ gate, float* __restrict__ resid, int H, int k) {
     const int t = blockIdx.x;
     float* r = resid + (long long)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += blockDim.x * gridDim.y) {
         float acc = 0.f;
         for (int j = 0; j < k; ++j)
             acc = fmaf(wts[t * k + j], y[(long long)dest[t * k + j] * H + i], acc);
@@ -172,12 +174,16 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
               "rope: rotary_dim must be even and in 2..head_dim");
     int* err = error_flag_ptr();
     const int threads = 256;
+    const int work = (nh + nkv) * hd;
+    int slices = (work + threads - 1) / threads;
+    if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
+    dim3 grid(T, slices);
     if (dtype == F32)
-        rope_kv_write_kernel<float><<<T, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), nh, nkv, hd,
             page_size, total_pages, err);
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
     check_launch("rope_kv_write");
@@ -186,7 +192,9 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
 void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
                  float* resid, int T, int H, int k, cudaStream_t stream) {
     if (T <= 0) return;
-    moe_combine_kernel<<<T, 256, 0, stream>>>(y, dest, wts, shared, gate, resid, H, k);
+    int slices = (H + 255) / 256;
+    if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
+    moe_combine_kernel<<<dim3(T, slices), 256, 0, stream>>>(y, dest, wts, shared, gate, resid, H, k);
     check_launch("moe_combine");
 }
 

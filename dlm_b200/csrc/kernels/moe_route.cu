@@ -6,11 +6,27 @@ namespace dlmk {
 
 namespace {
 
-constexpr int ROUTER_THREADS = 128;
+constexpr int ROUTER_THREADS = 256;
 
-// One block per token.  Each expert's logit is one warp's dot product summed in a fixed order,
-// so routing does not depend on what else is in the batch.
-template <typename T>
+// 8 consecutive elements of a row as floats (one 16-byte load for bfloat16, two for float32).
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// One block per token.  Each expert's logit is one warp's dot product summed in a fixed order
+// (lane l takes elements 8l..8l+7 of every 256, then a shuffle tree), so routing does not depend
+// on what else is in the batch.  VEC: rows are 16-byte aligned and H is a multiple of 8.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const T* __restrict__ h, const T* __restrict__ w, int32_t* __restrict__ ids,
                    float* __restrict__ wts, float* __restrict__ gate, int H, int E, int k, int norm, int has_gate) {
@@ -25,7 +41,18 @@ router_topk_kernel(const T* __restrict__ h, const T* __restrict__ w, int32_t* __
     for (int e = warp; e < rows; e += nwarp) {
         const T* wr = w + (long long)e * H;
         float s = 0.f;
-        for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
+        if (VEC) {
+            for (int i = lane * 8; i < H; i += 256) {
+                float wv[8];
+                load8(wr + i, wv);
+                const float4 xa = *reinterpret_cast<const float4*>(x + i), xb = *reinterpret_cast<const float4*>(x + i + 4);
+                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s = fmaf(xv[j], wv[j], s);
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
+        }
         s = warp_sum(s);
         if (lane == 0) prob[e] = s;
     }
@@ -121,18 +148,18 @@ void router_topk(const void* h, const void* w, int32_t* ids, float* wts, float* 
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
     const size_t smem = sizeof(float) * (size_t)(H + E + 1);
     DLM_CHECK(smem <= 200 * 1024, "router: hidden_size + num_experts does not fit in shared memory");
-    if (dtype == F32) {
-        auto kern = router_topk_kernel<float>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<T, ROUTER_THREADS, smem, stream>>>(static_cast<const float*>(h), static_cast<const float*>(w), ids,
-                                                  wts, gate, H, E, k, norm, has_gate);
-    } else {
-        auto kern = router_topk_kernel<__nv_bfloat16>;
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kern<<<T, ROUTER_THREADS, smem, stream>>>(static_cast<const __nv_bfloat16*>(h),
-                                                  static_cast<const __nv_bfloat16*>(w), ids, wts, gate, H, E, k, norm,
-                                                  has_gate);
+    const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+#define DLM_ROUTER(T, VEC)                                                                                   \
+    {                                                                                                        \
+        auto kern = router_topk_kernel<T, VEC>;                                                              \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
+        kern<<<T_, ROUTER_THREADS, smem, stream>>>(static_cast<const T*>(h), static_cast<const T*>(w), ids,  \
+                                                   wts, gate, H, E, k, norm, has_gate);                      \
     }
+    const int T_ = T;
+    if (dtype == F32) { if (vec) DLM_ROUTER(float, true) else DLM_ROUTER(float, false) }
+    else { if (vec) DLM_ROUTER(__nv_bfloat16, true) else DLM_ROUTER(__nv_bfloat16, false) }
+#undef DLM_ROUTER
     check_launch("router_topk");
 }
 

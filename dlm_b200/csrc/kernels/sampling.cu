@@ -60,6 +60,44 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
     if (threadIdx.x == 0) out[blockIdx.x] = ri == 0x7fffffff ? 0 : ri;
 }
 
+// Two stages for a large vocabulary: every block finds the first maximum of its chunk, then one
+// warp per row picks among the chunks (lower chunk first on ties, so the first maximum overall).
+constexpr int ARGMAX_CHUNKS = 32;
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ pv,
+                                                             int32_t* __restrict__ pi, int V) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int row = blockIdx.x, c = blockIdx.y;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = c * per, hi = min(V, lo + per);
+    const float* r = logits + (long long)row * V;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = r[i];
+        if (v > bv) { bv = v; bi = i; }
+    }
+    float rv;
+    int ri;
+    block_argmax(bv, bi, sv, si, rv, ri);
+    if (threadIdx.x == 0) { pv[row * ARGMAX_CHUNKS + c] = rv; pi[row * ARGMAX_CHUNKS + c] = ri; }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int32_t* __restrict__ pi,
+                                    int32_t* __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float v = pv[row * ARGMAX_CHUNKS + lane];
+    int i = pi[row * ARGMAX_CHUNKS + lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+    if (lane == 0) out[row] = i == 0x7fffffff ? 0 : i;
+}
+
 enum SelectMode { COUNT = 0, MASS_GE = 1, MASS_GT = 2 };
 
 struct RowView {
@@ -209,10 +247,20 @@ sample_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
 
 }  // namespace
 
-void argmax(const float* logits, int32_t* out, int N, int V, cudaStream_t stream) {
+size_t argmax_scratch_bytes(int N, int V) { return V >= 16384 ? (size_t)N * ARGMAX_CHUNKS * 8 : 0; }
+
+void argmax(const float* logits, int32_t* out, int N, int V, void* scratch, cudaStream_t stream) {
     if (N <= 0) return;
     DLM_CHECK(V > 0, "argmax: empty vocabulary");
-    argmax_kernel<<<N, THREADS, 0, stream>>>(logits, out, V);
+    static_assert(ARGMAX_CHUNKS == 32, "the final stage is one warp");
+    if (V >= 16384 && scratch != nullptr) {
+        float* pv = static_cast<float*>(scratch);
+        int32_t* pi = reinterpret_cast<int32_t*>(pv + (size_t)N * ARGMAX_CHUNKS);
+        argmax_partial_kernel<<<dim3(N, ARGMAX_CHUNKS), 256, 0, stream>>>(logits, pv, pi, V);
+        argmax_final_kernel<<<N, 32, 0, stream>>>(pv, pi, out);
+    } else {
+        argmax_kernel<<<N, THREADS, 0, stream>>>(logits, out, V);
+    }
     check_launch("argmax");
 }
 

@@ -57,6 +57,12 @@ class Engine:
         self.scheduler = host.Scheduler(self.cache.manager, host.SchedulerConfig(
             max_step_tokens=int(max_step_tokens), max_step_requests=int(max_requests),
             max_context=self.max_context, vocab_size=int(model.spec.vocab_size)))
+        # replayed CUDA graphs of pure decode steps, keyed by (rows, bucket of the longest request)
+        # (not for models with per-request state: building a graph runs its step once more)
+        self.use_graphs = (self.rt.device.type == "cuda" and hasattr(self.rt.ops, "launches")
+                           and not self.cache.state)
+        self._graphs: dict[tuple[int, int], dict] = {}
+        self._graph_pool = None
         self._samplers: dict[int, RequestSampler] = {}
         self._results: dict[int, list[int]] = {}
         self._reasons: dict[int, str] = {}
@@ -102,6 +108,55 @@ class Engine:
         batch = self.cache.make_batch(items)
         return self.model.step(batch, self.cache)
 
+    # ------------------------------------------------- replayed decode steps
+    def _decode_graph(self, rows: int, bucket: int, items) -> dict:
+        """The captured graph of a decode step of `rows` requests none of which holds more than
+        `bucket` tokens: the step function and the arg-max over its logits.  Everything the kernels
+        read that changes from step to step lies in one device buffer of fixed layout."""
+        key = (rows, bucket)
+        ent = self._graphs.get(key)
+        if ent is not None:
+            return ent
+        cache, ops = self.cache, self.rt.ops
+        width = -(-self.max_context // cache.page_size)
+        host = cache.host
+        sitems = [host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
+        lay = cache.manager.plan_layout(sitems, width)
+        meta = torch.zeros(lay.total, dtype=torch.int32, device=self.rt.device)
+        batch = cache.batch_from_layout(lay, meta)
+        batch.max_kv_len = bucket
+        cache.fill_metadata(sitems, lay, meta)
+        # once eagerly (first-call set-up of the kernels must not fall into the capture), then capture
+        torch.cuda.synchronize()
+        ops.argmax(self.model.step(batch, cache))
+        torch.cuda.synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.step(batch, cache)
+            tokens = ops.argmax(logits)
+        ent = dict(graph=graph, layout=lay, meta=meta, logits=logits, tokens=tokens,
+                   launches=ops.launches - before, width=width)
+        self._graphs[key] = ent
+        return ent
+
+    def _run_decode(self, items):
+        """A pure decode step through its graph.  Returns (logits, greedy tokens) on the device."""
+        longest = max(self.cache.manager.length(s) for s, _, _ in items)
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        bucket = min(bucket, max(self.max_context, longest))
+        ent = self._decode_graph(len(items), bucket, items)
+        host = self.cache.host
+        sitems = [host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
+        self.cache.fill_metadata(sitems, ent["layout"], ent["meta"])
+        ent["graph"].replay()
+        self.rt.ops.launches += ent["launches"]
+        return ent["logits"], ent["tokens"]
+
     # ------------------------------------------------------------- generation
     def submit(self, prompt: Iterable[int], params: SamplingParams | None = None, max_new_tokens: int = 16,
                eos_token=None) -> int:
@@ -137,10 +192,18 @@ class Engine:
             if it.start == 0:
                 self.cache.reset_state(it.slot)
         items = [(it.slot, it.tokens, [len(it.tokens) - 1] if it.sample else []) for it in plan.items]
-        logits = self._run(items)
-        self.last_logits = logits
         rows = [it for it in plan.items if it.sample]
-        tokens = sample_rows(self.rt.ops, logits, [self._samplers[it.id] for it in rows])
+        samplers = [self._samplers[it.id] for it in rows]
+        if self.use_graphs and all(len(it.tokens) == 1 and it.sample for it in plan.items):
+            logits, greedy = self._run_decode(items)
+            if all(s.params.plain_greedy for s in samplers):
+                tokens = greedy.tolist()
+            else:
+                tokens = sample_rows(self.rt.ops, logits, samplers)
+        else:
+            logits = self._run(items)
+            tokens = sample_rows(self.rt.ops, logits, samplers)
+        self.last_logits = logits
         self.rt.ops.check_errors()
         for it, tok in zip(rows, tokens):
             self._samplers[it.id].note(tok)

@@ -172,8 +172,10 @@ class NativeOps:
     def argmax(self, logits):
         N, V = logits.shape
         out = torch.empty((N,), dtype=torch.int32, device=logits.device)
-        self.launches += 1
-        self.k.argmax(_p(logits), _p(out), N, V, self._stream())
+        nbytes = self.k.argmax_scratch_bytes(N, V)
+        scratch = torch.empty((nbytes,), dtype=torch.uint8, device=logits.device) if nbytes else None
+        self.launches += 2 if nbytes else 1
+        self.k.argmax(_p(logits), _p(out), N, V, _p(scratch), self._stream())
         return out
 
     def sample(self, logits, params, top_k, u, seen_offsets, seen_tokens):
