@@ -131,6 +131,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference()
@@ -213,6 +214,20 @@ def main() -> int:
         eng.scheduler.drain_finished()
         return dict(dev_ms=dev_ms, e2e_s=w1 - w0, produced=produced, launches=launches, clocks=clocks, ctx=ctx)
 
+    if args.only_prefill:
+        T = 2048
+        times = []
+        for it in range(3):
+            s = eng.cache.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([(s, prompts(1, T)[0], [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            eng.cache.close(s)
+        print(json.dumps({"prefill_ms": [round(t, 3) for t in times], "tokens": T, "layers": args.layers}))
+        return 0
     main_run = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
     ms_per_step = main_run["dev_ms"] / args.steps
     value = args.batch * args.steps / (main_run["dev_ms"] / 1e3)

@@ -24,9 +24,14 @@ void attention(const void* q, const void* k_cache, const void* v_cache, const in
         attention_decode(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, scratch, R, nh, nkv, hd,
                          page_size, total_pages, window, scale, n_splits, chunk, dtype, stream);
     }
-    if (!decode || num_single < R)
-        attention_simt(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd, page_size,
-                       total_pages, window, scale, decode ? 1 : 0, dtype, stream);
+    if (!decode || num_single < R) {
+        if (fast && dtype == BF16 && attention_prefill_ok(hd))
+            attention_prefill(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd,
+                              page_size, total_pages, window, scale, decode ? 1 : 0, stream);
+        else
+            attention_simt(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd,
+                           page_size, total_pages, window, scale, decode ? 1 : 0, dtype, stream);
+    }
     (void)max_q_len;
 }
 

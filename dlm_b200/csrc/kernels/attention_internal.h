@@ -14,6 +14,13 @@ void attention_simt(const void* q, const void* k_cache, const void* v_cache, con
                     int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
                     int dtype, cudaStream_t stream);
 
+// Tensor-core kernel (bfloat16) for the head sizes attention_prefill_ok names.
+bool attention_prefill_ok(int hd);
+void attention_prefill(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                       int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
+                       int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                       cudaStream_t stream);
+
 // Split-key decode kernel for requests with exactly one query token (bfloat16 and float32).
 bool attention_decode_ok(int hd);
 void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk);

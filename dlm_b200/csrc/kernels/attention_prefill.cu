@@ -1,0 +1,289 @@
+// Prefill attention on the warp-level tensor-core path (bfloat16): portions of prompts, each
+// query attending to its request's paged keys up to its own position (optionally only the
+// last `window` of them).
+//
+// One block = 64 consecutive query tokens of one request x one query head; 4 warps of 16 rows.
+// Keys and values come in tiles of 64 (aligned to absolute positions), two tiles in flight
+// through asynchronous 16-byte copies; S = Q K^T and O += P V are mma.sync m16n8k16 with
+// 32-bit accumulation; the softmax runs in 32-bit on the accumulator registers, whose layout
+// is already that of the next product's left operand.  Requests with a single query token are
+// left to the decode kernel when it runs.
+#include "api.h"
+#include "attention_internal.h"
+#include "common.cuh"
+
+namespace dlmk {
+
+namespace {
+
+constexpr int BQ = 64, BKV = 64, WARPS = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                         const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
+                         int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
+                         __nv_bfloat16* __restrict__ out, int R, int nh, int nkv, int page_size, int total_pages,
+                         int window, float scale_log2, int skip_single, int* err) {
+    constexpr int PITCH = HD + 8;              // elements per shared-memory row (16 bytes of padding)
+    constexpr int KS = HD / 16;                // k16 steps over the head dimension
+    constexpr int DT = HD / 8;                 // n8 tiles of the output
+    constexpr int CPR = HD / 8;                // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BQ][PITCH]
+    __nv_bfloat16* Ks = Qs + BQ * PITCH;                                 // [2][BKV][PITCH]
+    __nv_bfloat16* Vs = Ks + 2 * BKV * PITCH;                            // [2][BKV][PITCH]
+    __shared__ int s_map[2];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int head = blockIdx.y, kvh = head / (nh / nkv);
+    if (tid == 0) {
+        int acc = 0;
+        s_map[0] = -1;
+        for (int r = 0; r < R; ++r) {
+            const int ql = cu_q[r + 1] - cu_q[r];
+            const int tiles = (skip_single && ql == 1) ? 0 : (ql + BQ - 1) / BQ;
+            if ((int)blockIdx.x < acc + tiles) {
+                s_map[0] = r;
+                s_map[1] = ((int)blockIdx.x - acc) * BQ;
+                break;
+            }
+            acc += tiles;
+        }
+    }
+    __syncthreads();
+    const int r = s_map[0];
+    if (r < 0) return;
+    const int q0 = s_map[1];
+    const int q_begin = cu_q[r], q_len = cu_q[r + 1] - q_begin;
+    const int n_q = min(BQ, q_len - q0);
+    const int len = kv_len[r];
+    const int pos0 = len - q_len + q0;
+    const int Q = nh * HD;
+    const int32_t* table = block_table + (long long)r * table_width;
+
+    // the query tile (rows beyond the portion are zero)
+    for (int idx = tid; idx < BQ * CPR; idx += WARPS * 32) {
+        const int row = idx / CPR, c = idx % CPR;
+        if (row < n_q) cp_async16(Qs + row * PITCH + c * 8, q + (long long)(q_begin + q0 + row) * Q + head * HD + c * 8);
+        else *reinterpret_cast<uint4*>(Qs + row * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    const int hi = pos0 + n_q - 1;
+    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int t_begin = (lo / BKV) * BKV;
+    const int n_tiles = (hi - t_begin) / BKV + 1;
+
+    auto fill = [&](int stage, int j0) {
+        __nv_bfloat16* kd = Ks + (size_t)stage * BKV * PITCH;
+        __nv_bfloat16* vd = Vs + (size_t)stage * BKV * PITCH;
+        for (int idx = tid; idx < BKV * CPR; idx += WARPS * 32) {
+            const int key = idx / CPR, c = idx % CPR;
+            const int j = j0 + key;
+            int page = -1;
+            if (j >= lo && j <= hi) {
+                const int lp = j / page_size;
+                page = lp < table_width ? table[lp] : -1;
+                if (page < 0 || page >= total_pages) { *err = 3; page = -1; }
+            }
+            if (page >= 0) {
+                const long long off = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * HD + c * 8;
+                cp_async16(kd + key * PITCH + c * 8, k_cache + off);
+                cp_async16(vd + key * PITCH + c * 8, v_cache + off);
+            } else {
+                *reinterpret_cast<uint4*>(kd + key * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + key * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fill(0, t_begin);
+
+    const int g = lane >> 2, t = lane & 3;
+    const int lm_row = lane & 15, lm_col = (lane >> 4) * 8;
+    const int row_a = warp * 16 + g, row_b = row_a + 8;          // this thread's two query rows in the tile
+    const int pa = pos0 + row_a, pb = pos0 + row_b;
+
+    uint32_t qf[KS][4];
+    float o[DT][4];
+#pragma unroll
+    for (int i = 0; i < DT; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it & 1;
+        const int j0 = t_begin + it * BKV;
+        if (it + 1 < n_tiles) {
+            fill(stage ^ 1, j0 + BKV);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        if (it == 0) {
+#pragma unroll
+            for (int kk = 0; kk < KS; ++kk) ldsm_x4(qf[kk], Qs + (warp * 16 + lm_row) * PITCH + kk * 16 + lm_col);
+        }
+        const __nv_bfloat16* kt = Ks + (size_t)stage * BKV * PITCH;
+        const __nv_bfloat16* vt = Vs + (size_t)stage * BKV * PITCH;
+
+        // S = Q K^T for 16 rows x 64 keys
+        float s[BKV / 8][4];
+#pragma unroll
+        for (int j = 0; j < BKV / 8; ++j)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+            for (int jn = 0; jn < BKV / 16; ++jn) {
+                uint32_t kf[4];
+                ldsm_x4(kf, kt + (jn * 16 + lm_row) * PITCH + kk * 16 + lm_col);
+                mma16816(s[2 * jn], qf[kk], kf[0], kf[2]);
+                mma16816(s[2 * jn + 1], qf[kk], kf[1], kf[3]);
+            }
+        }
+        // mask, scale (to base 2), running maximum
+        float mx_a = m_a, mx_b = m_b;
+#pragma unroll
+        for (int j = 0; j < BKV / 8; ++j) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = j0 + j * 8 + 2 * t + (c & 1);
+                const int p = (c < 2) ? pa : pb;
+                const bool vis = key <= p && (window <= 0 || p - key < window) && key >= lo;
+                const float v = vis ? s[j][c] * scale_log2 : -INFINITY;
+                s[j][c] = v;
+                if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        // a row that has seen nothing yet keeps its state (exp2(-inf - -inf) must not appear)
+        const float base_a = mx_a == -INFINITY ? 0.f : mx_a, base_b = mx_b == -INFINITY ? 0.f : mx_b;
+        const float al_a = exp2f(m_a - base_a), al_b = exp2f(m_b - base_b);     // m = -inf: 0
+        float sum_a = 0.f, sum_b = 0.f;
+        uint32_t pf[BKV / 16][4];
+#pragma unroll
+        for (int j = 0; j < BKV / 8; ++j) {
+            const float p0 = exp2f(s[j][0] - base_a), p1 = exp2f(s[j][1] - base_a);
+            const float p2 = exp2f(s[j][2] - base_b), p3 = exp2f(s[j][3] - base_b);
+            sum_a += p0 + p1;
+            sum_b += p2 + p3;
+            // accumulator tiles 2k and 2k + 1 are the left operand of the k-th 16-key step of P V
+            pf[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+            pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+        l_a = l_a * al_a + sum_a;
+        l_b = l_b * al_b + sum_b;
+        m_a = mx_a;
+        m_b = mx_b;
+#pragma unroll
+        for (int i = 0; i < DT; ++i) {
+            o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+#pragma unroll
+            for (int dn = 0; dn < HD / 16; ++dn) {
+                uint32_t vf[4];
+                ldsm_x4_trans(vf, vt + (kk * 16 + lm_row) * PITCH + dn * 16 + lm_col);
+                mma16816(o[2 * dn], pf[kk], vf[0], vf[1]);
+                mma16816(o[2 * dn + 1], pf[kk], vf[2], vf[3]);
+            }
+        }
+        __syncthreads();
+    }
+
+    const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+#pragma unroll
+    for (int i = 0; i < DT; ++i) {
+        const int d = i * 8 + 2 * t;
+        if (row_a < n_q)
+            *reinterpret_cast<uint32_t*>(out + (long long)(q_begin + q0 + row_a) * Q + head * HD + d) =
+                pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
+        if (row_b < n_q)
+            *reinterpret_cast<uint32_t*>(out + (long long)(q_begin + q0 + row_b) * Q + head * HD + d) =
+                pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
+    }
+}
+
+template <int HD>
+void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
+            const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int R,
+            int nh, int nkv, int page_size, int total_pages, int window, float scale, int skip_single) {
+    const size_t smem = (size_t)(BQ + 4 * BKV) * (HD + 8) * sizeof(__nv_bfloat16);
+    auto kern = attention_prefill_kernel<HD>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, WARPS * 32, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
+        static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
+        static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, window,
+        scale * 1.4426950408889634f, skip_single, error_flag_ptr());
+}
+
+}  // namespace
+
+bool attention_prefill_ok(int hd) {
+    return hd == 16 || hd == 32 || hd == 48 || hd == 64 || hd == 96 || hd == 128;
+}
+
+void attention_prefill(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                       int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
+                       int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                       cudaStream_t stream) {
+    if (T <= 0 || R <= 0) return;
+    DLM_CHECK(attention_prefill_ok(hd), "prefill attention: this head_dim has no tensor-core kernel");
+    DLM_CHECK(nh % nkv == 0, "attention: heads must be a multiple of kv heads");
+    dim3 grid((T + BQ - 1) / BQ + R, nh);
+#define DLM_PREFILL(HD)                                                                                             \
+    launch<HD>(grid, stream, q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, R, nh, nkv, page_size, \
+               total_pages, window, scale, skip_single)
+    switch (hd) {
+        case 16: DLM_PREFILL(16); break;
+        case 32: DLM_PREFILL(32); break;
+        case 48: DLM_PREFILL(48); break;
+        case 64: DLM_PREFILL(64); break;
+        case 96: DLM_PREFILL(96); break;
+        default: DLM_PREFILL(128); break;
+    }
+#undef DLM_PREFILL
+    check_launch("attention_prefill");
+}
+
+}  // namespace dlmk

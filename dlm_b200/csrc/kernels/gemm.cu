@@ -15,11 +15,18 @@ void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw,
                             epilogue, M, stream);
                 return;
             }
+            gemm_mma(a, lda, a_rows, w, ldw, w_expert_stride, nullptr, 0, bias, out, ldo, M, N, K, out_dtype, epilogue,
+                     stream);
+            return;
         } else if (bias == nullptr && (long long)M <= 16LL * num_experts) {
             // few rows per expert on average: stream each active expert's weights once
             const int avg2 = (2 * M + num_experts - 1) / num_experts;     // twice the mean rows per expert
             gemm_smallm(a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, nullptr, out, ldo, M, N,
                         K, out_dtype, epilogue, avg2 <= 4 ? 8 : (avg2 <= 16 ? 16 : 32), stream);
+            return;
+        } else if (bias == nullptr) {
+            gemm_mma(a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, nullptr, out, ldo, M, N, K,
+                     out_dtype, epilogue, stream);
             return;
         }
     }

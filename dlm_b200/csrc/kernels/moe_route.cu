@@ -26,16 +26,30 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
 // One block per token.  Each expert's logit is one warp's dot product summed in a fixed order
 // (lane l takes elements 8l..8l+7 of every 256, then a shuffle tree), so routing does not depend
 // on what else is in the batch.  VEC: rows are 16-byte aligned and H is a multiple of 8.
-template <typename T, bool VEC>
+// With norm_w != nullptr the input is the 32-bit residual and the RMS norm (weight norm_w, eps)
+// is applied here, in 32-bit, so that the router never sees a rounded activation.
+template <typename TX, typename T, bool VEC>
 __global__ void __launch_bounds__(ROUTER_THREADS)
-router_topk_kernel(const T* __restrict__ h, const T* __restrict__ w, int32_t* __restrict__ ids,
-                   float* __restrict__ wts, float* __restrict__ gate, int H, int E, int k, int norm, int has_gate) {
+router_topk_kernel(const TX* __restrict__ h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
+                   int32_t* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int H, int E, int k,
+                   int norm, int has_gate) {
     extern __shared__ float smem[];
+    __shared__ float scratch[32];
     float* x = smem;            // [H]
     float* prob = x + H;        // [E + 1]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nwarp = blockDim.x >> 5;
-    for (int i = tid; i < H; i += blockDim.x) x[i] = to_f32(h[(long long)t * H + i]);
+    float ss = 0.f;
+    for (int i = tid; i < H; i += blockDim.x) {
+        const float v = to_f32(h[(long long)t * H + i]);
+        x[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (norm_w != nullptr) {
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+        for (int i = tid; i < H; i += blockDim.x) x[i] = (x[i] * inv) * norm_w[i];
+    }
     __syncthreads();
     const int rows = E + (has_gate ? 1 : 0);
     for (int e = warp; e < rows; e += nwarp) {
@@ -142,23 +156,25 @@ moe_permute_kernel(const int32_t* __restrict__ ids, int n, int k, int E, int32_t
 
 }  // namespace
 
-void router_topk(const void* h, const void* w, int32_t* ids, float* wts, float* gate, int T, int H, int E, int k,
-                 int norm, int has_gate, int dtype, cudaStream_t stream) {
+void router_topk(const void* h, const void* w, const float* norm_w, float eps, int32_t* ids, float* wts, float* gate,
+                 int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
     const size_t smem = sizeof(float) * (size_t)(H + E + 1);
     DLM_CHECK(smem <= 200 * 1024, "router: hidden_size + num_experts does not fit in shared memory");
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-#define DLM_ROUTER(T, VEC)                                                                                   \
-    {                                                                                                        \
-        auto kern = router_topk_kernel<T, VEC>;                                                              \
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
-        kern<<<T_, ROUTER_THREADS, smem, stream>>>(static_cast<const T*>(h), static_cast<const T*>(w), ids,  \
-                                                   wts, gate, H, E, k, norm, has_gate);                      \
+#define DLM_ROUTER(TX, T, VEC)                                                                                \
+    {                                                                                                         \
+        auto kern = router_topk_kernel<TX, T, VEC>;                                                           \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
+        kern<<<T_, ROUTER_THREADS, smem, stream>>>(static_cast<const TX*>(h), static_cast<const T*>(w), norm_w, \
+                                                   eps, ids, wts, gate, H, E, k, norm, has_gate);             \
     }
     const int T_ = T;
-    if (dtype == F32) { if (vec) DLM_ROUTER(float, true) else DLM_ROUTER(float, false) }
-    else { if (vec) DLM_ROUTER(__nv_bfloat16, true) else DLM_ROUTER(__nv_bfloat16, false) }
+    // with norm_w the activations are the 32-bit residual whatever the weights' dtype
+    if (dtype == F32) { if (vec) DLM_ROUTER(float, float, true) else DLM_ROUTER(float, float, false) }
+    else if (norm_w != nullptr) { if (vec) DLM_ROUTER(float, __nv_bfloat16, true) else DLM_ROUTER(float, __nv_bfloat16, false) }
+    else { if (vec) DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, false) }
 #undef DLM_ROUTER
     check_launch("router_topk");
 }

@@ -141,15 +141,17 @@ class NativeOps:
         return out
 
     # ------------------------------------------------------------------- moe
-    def router_topk(self, h, w, E, k, norm, has_gate):
+    def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0):
+        """With ``norm_weight`` given, ``h`` is the 32-bit residual and the RMS norm runs inside the kernel."""
         T, H = h.shape
         assert w.shape == (E + (1 if has_gate else 0), H)
+        assert (norm_weight is None and h.dtype == w.dtype) or (norm_weight is not None and h.dtype == torch.float32)
         ids = torch.empty((T, k), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, k), dtype=torch.float32, device=h.device)
         gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
         self.launches += 1
-        self.k.router_topk(_p(h), _p(w), _p(ids), _p(wts), _p(gate), T, H, E, k, int(norm), int(has_gate),
-                           _dt(h.dtype), self._stream())
+        self.k.router_topk(_p(h), _p(w), _p(norm_weight), float(eps), _p(ids), _p(wts), _p(gate), T, H, E, k,
+                           int(norm), int(has_gate), _dt(w.dtype), self._stream())
         return ids, wts, gate
 
     def moe_permute(self, ids, E):

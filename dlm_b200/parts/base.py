@@ -7,7 +7,7 @@ learns which model it is in.  It names its tensors relative to itself
 * ``Norm``              ``forward(x_f32, rt, rows=None) -> activations``
 * ``PositionEncoding``  gives the rotation table the attention kernels apply
 * ``Mixer``             ``forward(h, resid, ctx, call)``: adds its output to ``resid``
-* ``FeedForward``       ``forward(h, resid, ctx)``: adds its output to ``resid``
+* ``FeedForward``       ``forward(h, resid, ctx, pre_norm)``: adds its output to ``resid``
 
 and a ``Block`` arranges one mixer, one feed-forward and their norms.
 
@@ -114,7 +114,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    def forward(self, h: torch.Tensor, resid: torch.Tensor, ctx: "StepContext") -> None:
+    def forward(self, h: torch.Tensor, resid: torch.Tensor, ctx: "StepContext", pre_norm: "Norm | None" = None) -> None:
+        """``pre_norm`` is the norm that produced ``h`` from ``resid``; a part that needs the
+        normalised input in 32-bit (a router) may apply it again to the residual itself."""
         raise NotImplementedError
 
 

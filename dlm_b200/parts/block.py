@@ -38,7 +38,7 @@ class PreNormBlock(Part):
     def forward(self, resid, ctx: StepContext, call: int):
         rt = ctx.rt
         self.mixer.forward(self.norm1.forward(resid, rt), resid, ctx, call)
-        self.ffn.forward(self.norm2.forward(resid, rt), resid, ctx)
+        self.ffn.forward(self.norm2.forward(resid, rt), resid, ctx, pre_norm=self.norm2)
 
 
 register_part("block", "prenorm", PreNormBlock)

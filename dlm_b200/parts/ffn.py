@@ -5,6 +5,7 @@ import torch
 
 from ..registry import register_part
 from .base import FeedForward, ParamSpec, Runtime, StepContext
+from .norm import RMSNorm
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -32,7 +33,7 @@ class DenseSwiGLU(FeedForward):
         self.w_gate_up = interleave_gate_up(rt.matrix(tensors["gate_proj.weight"]), rt.matrix(tensors["up_proj.weight"]))
         self.w_down = rt.matrix(tensors["down_proj.weight"])
 
-    def forward(self, h, resid, ctx: StepContext):
+    def forward(self, h, resid, ctx: StepContext, pre_norm=None):
         ops = ctx.rt.ops
         act = ops.linear_swiglu(h, self.w_gate_up)
         ops.linear_add(act, self.w_down, resid)
@@ -40,7 +41,7 @@ class DenseSwiGLU(FeedForward):
 
 class SoftmaxTopKMoE(FeedForward):
     """Routed experts as the reference computes them (src/forward/cpu.rs:980-1048): router
-    logits in 32-bit, softmax over all experts, the k largest probabilities (ties: lower
+    logits in 32-bit from the 32-bit normalised residual, softmax over all experts, the k largest probabilities (ties: lower
     expert first), optionally renormalised; each chosen expert's SwiGLU output scaled by its
     weight and summed from zero in routing order; then an optional shared expert scaled by
     ``sigmoid(shared_gate · h)`` (1 when ``shared_gate`` is False); the sum goes to the residual.
@@ -88,9 +89,14 @@ class SoftmaxTopKMoE(FeedForward):
                                                  rt.matrix(tensors["shared_expert.up_proj.weight"]))
             self.ws_down = rt.matrix(tensors["shared_expert.down_proj.weight"])
 
-    def forward(self, h, resid, ctx: StepContext):
+    def forward(self, h, resid, ctx: StepContext, pre_norm=None):
         ops = ctx.rt.ops
-        ids, wts, gate = ops.router_topk(h, self.w_router, self.E, self.k, self.norm, self.has_gate)
+        if isinstance(pre_norm, RMSNorm):
+            # router logits (and the shared expert's gate) from the 32-bit normalised residual
+            ids, wts, gate = ops.router_topk(resid, self.w_router, self.E, self.k, self.norm, self.has_gate,
+                                             norm_weight=pre_norm.weight, eps=pre_norm.eps)
+        else:
+            ids, wts, gate = ops.router_topk(h, self.w_router, self.E, self.k, self.norm, self.has_gate)
         offsets, rows, dest = ops.moe_permute(ids, self.E)
         act = ops.grouped_swiglu(h, self.w_gate_up, offsets, rows)
         y = ops.grouped_linear(act, self.w_down, offsets)

@@ -122,7 +122,9 @@ class PlainOps:
         return out.to(q.dtype)
 
     # ------------------------------------------------------------------- moe
-    def router_topk(self, h, w, E, k, norm, has_gate):
+    def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0):
+        if norm_weight is not None:
+            h = self.rmsnorm(h, norm_weight, eps, torch.float32)
         logits = _f(h) @ _f(w).T
         gate = None
         if has_gate:

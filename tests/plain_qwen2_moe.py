@@ -13,8 +13,9 @@ the docstrings below.
 
 ``emulate_bf16=True`` rounds to bfloat16 at the places where the engine's
 bfloat16 path stores bfloat16 (matrices, normed activations, rotated q/k, v,
-attention output, the SwiGLU product); sums, softmax, norms, router logits,
-rotation angles and the residual stay in ``compute`` precision.
+attention output, the SwiGLU product); sums, softmax, norms, router logits (taken
+from the unrounded normalised residual), rotation angles and the residual stay in
+``compute`` precision.
 """
 from __future__ import annotations
 
@@ -166,11 +167,12 @@ def route_topk(logits: torch.Tensor, k: int, norm: bool):
 MARGIN_LOG = None
 
 
-def moe_ffn(x, lw, cfg: PlainConfig, rnd):
+def moe_ffn(x, lw, cfg: PlainConfig, rnd, x_router=None):
     """src/forward/cpu.rs:1005-1048: routed experts summed from zero in routing order, each
     scaled by its gate weight; then the shared expert scaled by sigmoid(gate·x) (1 when the
     gate tensor is absent)."""
-    logits = x @ lw["router"].T
+    xr = x if x_router is None else x_router      # the router's input: the unrounded normalised residual
+    logits = xr @ lw["router"].T
     ids, wts = route_topk(logits, cfg.k, cfg.norm_topk)
     if MARGIN_LOG is not None and cfg.k < cfg.E:
         sp = torch.sort(softmax(logits), dim=-1, descending=True).values
@@ -187,7 +189,7 @@ def moe_ffn(x, lw, cfg: PlainConfig, rnd):
         g, u, d = lw["shared"]
         sh = swiglu_ffn(x, g, u, d, rnd)
         if lw.get("shared_gate") is not None:
-            gate = 1.0 / (1.0 + torch.exp(-(x @ lw["shared_gate"].T)))     # [T, 1]
+            gate = 1.0 / (1.0 + torch.exp(-(xr @ lw["shared_gate"].T)))    # [T, 1]
         else:
             gate = torch.ones(x.shape[0], 1, dtype=x.dtype)
         out = out + gate * sh
@@ -210,9 +212,10 @@ def decoder_layer(x, lw, cfg: PlainConfig, layer_index: int, positions, inv_freq
     v = rnd(v.view(T, cfg.nkv, cfg.hd))
     ctx = rnd(attention(q, k, v, cfg.layer_window(layer_index)).reshape(T, cfg.nh * cfg.hd))
     x = x + ctx @ lw["o"].T
-    n2 = rnd(rmsnorm(x, lw["ln2"], cfg.eps))
+    n2_full = rmsnorm(x, lw["ln2"], cfg.eps)
+    n2 = rnd(n2_full)
     if "router" in lw:
-        x = x + moe_ffn(n2, lw, cfg, rnd)
+        x = x + moe_ffn(n2, lw, cfg, rnd, x_router=n2_full)
     else:
         g, u, d = lw["dense"]
         x = x + swiglu_ffn(n2, g, u, d, rnd)
@@ -282,8 +285,8 @@ class PlainModel:
     def router_margins(self, tokens) -> torch.Tensor:
         """For every position, the smallest gap over the routed layers between the probability
         of the last expert chosen and the first one rejected.  Top-k is discontinuous: where
-        this gap is within rounding, two correct implementations may route differently, and
-        everything after that position may differ; tests compare only up to there."""
+        this gap is within rounding, two correct implementations may route differently; tests
+        do not compare such positions."""
         global MARGIN_LOG
         MARGIN_LOG = []
         try:
@@ -294,11 +297,6 @@ class PlainModel:
         if not gaps:
             return torch.full((len(tokens),), float("inf"), dtype=torch.float64)
         return torch.stack([g.to(torch.float64) for g in gaps]).min(dim=0).values
-
-    def clear_prefix(self, tokens, min_margin: float) -> int:
-        """Number of leading positions whose routing margin is at least ``min_margin``."""
-        low = torch.nonzero(self.router_margins(tokens) < min_margin)
-        return int(low[0]) if low.numel() else len(tokens)
 
     def logits(self, tokens, layer_order=None) -> torch.Tensor:
         """src/generate.rs:328-331 at every position: rmsnorm with model.norm, then the head.

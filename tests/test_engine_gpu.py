@@ -5,7 +5,7 @@ import torch
 
 import cuttings
 import plain_qwen2_moe as plain
-from tiny_configs import TINY, pick_prompt, prompt
+from tiny_configs import TINY, prompt
 
 pytestmark = pytest.mark.gpu
 
@@ -17,9 +17,11 @@ TOL_F32 = 1e-4
 TOL_BF16 = 1e-2
 # Routing is a discontinuous choice.  Where the oracle's gap between the last expert chosen and
 # the first rejected is within the noise of the precision under test, a correct engine may
-# choose the other one, and every later position of that request then differs.  Positions are
-# compared up to the first such place.  The gaps are in probability (about 1/experts here):
-# bfloat16 activations move a router probability by a few 1e-5, 32-bit sums by about 1e-8.
+# choose the other one, and that position's logits then differ by far more than rounding.  Such
+# positions are not compared (later positions see the difference only through one key among
+# many and stay within the tolerance).  The gaps are in probability (about 1/experts here);
+# the router reads the 32-bit residual, which bfloat16 rounding upstream moves by a few 1e-5 (a
+# probability by less), 32-bit summation order by about 1e-8.
 MARGIN = {"float32": 1e-6, "bfloat16": 2e-4}
 
 LENGTHS = [1, 7, 16, 33, 70, 129]
@@ -56,14 +58,14 @@ _PICKED = {}
 
 
 def requests_of(name, dtype, oracles, lengths=LENGTHS, base=0):
-    """Seeded prompts of the given lengths, each with the number of leading positions that can
-    be compared with the oracle."""
+    """Seeded prompts of the given lengths, each with its per-position routing margins."""
     V = TINY[name]["cfg"]["vocab_size"]
     out = {}
     for i, n in enumerate(lengths):
         key = (name, dtype, base + i, n)
         if key not in _PICKED:
-            _PICKED[key] = pick_prompt(oracles(name, dtype), base + i, n, V, MARGIN[dtype])
+            toks = prompt(base + i, n, V)
+            _PICKED[key] = (toks, oracles(name, dtype).router_margins(toks))
         out[f"r{i}"] = _PICKED[key]
     return out
 
@@ -75,19 +77,18 @@ def tokens_of(reqs):
 def compare(got, oracle, reqs, dtype):
     tol = TOL_F32 if dtype == "float32" else TOL_BF16
     compared = total = 0
-    for rid, (toks, clear) in reqs.items():
+    for rid, (toks, margins) in reqs.items():
         ref = oracle.logits(toks)
         total += len(toks)
         for p in range(len(toks)):
             assert (rid, p) in got, f"no logits for {rid} position {p}"
-            if p >= clear:
+            if float(margins[p]) < MARGIN[dtype]:
                 continue
             d = float((got[(rid, p)] - ref[p]).abs().max())
             assert d <= tol, f"request {rid} (length {len(toks)}) position {p}: max abs diff {d:.3e} > {tol}"
             compared += 1
-    # the comparison must not be empty: in 32-bit nearly every position qualifies; in bfloat16 the
-    # flat router of the smallest model leaves fewer (the 32-bit run covers the rest)
-    floor = 0.95 if dtype == "float32" else 0.25
+    # the comparison must not be empty
+    floor = 0.95 if dtype == "float32" else 0.5
     assert compared >= floor * total, f"only {compared} of {total} positions could be compared"
 
 
@@ -140,16 +141,19 @@ def test_first_tokens(name, dtype, engines, oracles):
 
 
 @pytest.mark.parametrize("name", list(TINY))
-def test_cuttings_agree_with_each_other_bf16(name, engines):
-    """Whatever the cut, the same position gives the same logits up to rounding: tighter
-    than the comparison with the oracle, because nothing but the batch shape differs."""
+def test_cuttings_agree_with_each_other_bf16(name, engines, oracles):
+    """Whatever the cut, the same position gives the same logits up to rounding (different
+    cuts run different kernels, which sum in different orders)."""
     V = TINY[name]["cfg"]["vocab_size"]
     reqs = {"a": prompt(70, 70, V), "b": prompt(71, 129, V)}
+    margins = {rid: oracles(name, "bfloat16").router_margins(t) for rid, t in reqs.items()}
     eng = engines(name, "bfloat16")
     a = cuttings.run_trace(eng, cuttings.whole(reqs))
     b = cuttings.run_trace(eng, cuttings.portions(reqs))
     c = cuttings.run_trace(eng, cuttings.tail_decode(reqs, 32))
     for key in a:
+        if float(margins[key[0]][key[1]]) < MARGIN["bfloat16"]:
+            continue
         assert float((a[key] - b[key]).abs().max()) <= TOL_BF16
         assert float((a[key] - c[key]).abs().max()) <= TOL_BF16
 

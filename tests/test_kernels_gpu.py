@@ -71,7 +71,8 @@ def test_rmsnorm_hand_value(ops):
 
 # ------------------------------------------------------------------------ products
 GEMM_SHAPES = [(1, 64, 64), (5, 97, 130), (64, 128, 256), (130, 200, 72), (257, 330, 1000), (3, 1408, 2048),
-               (8, 2048, 1408), (16, 100, 72), (33, 200, 200), (2, 48, 40), (9, 2816, 2048), (1, 300, 5632)]
+               (8, 2048, 1408), (16, 100, 72), (33, 200, 200), (2, 48, 40), (9, 2816, 2048), (1, 300, 5632),
+               (65, 128, 64), (300, 264, 40), (513, 2816, 2048), (1000, 96, 1408)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -98,7 +99,8 @@ def test_linear_add_and_swiglu(ops, ref, dtype, M, N, K):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("E,k,T,H,I", [(5, 1, 9, 72, 40), (8, 2, 33, 64, 32), (12, 3, 130, 256, 48),
-                                       (60, 4, 7, 512, 176), (12, 3, 20, 256, 48), (60, 4, 64, 2048, 1408)])
+                                       (60, 4, 7, 512, 176), (12, 3, 20, 256, 48), (60, 4, 64, 2048, 1408),
+                                       (8, 2, 700, 64, 32), (60, 4, 2048, 512, 176)])
 def test_grouped_products(ops, ref, dtype, E, k, T, H, I):
     h = rand((T, H), dtype, 9)
     g = torch.Generator().manual_seed(E)
@@ -147,6 +149,13 @@ def test_router(ops, ref, dtype, E, k, H, norm, gate):
     close(wts, wts2, rtol=1e-4, atol=1e-6)
     if gate:
         close(g, g2, rtol=1e-4, atol=1e-6)
+    # fused form: the 32-bit residual and the norm's weight go in, the norm runs inside
+    x = rand((T, H), torch.float32, 16, 2.0)
+    nw = 1 + rand((H,), torch.float32, 17, 0.1)
+    a = ops.router_topk(x, w, E, k, norm, gate, norm_weight=nw, eps=1e-6)
+    b = ref.router_topk(x, w, E, k, norm, gate, norm_weight=nw, eps=1e-6)
+    assert torch.equal(a[0], b[0])
+    close(a[1], b[1], rtol=1e-4, atol=1e-6)
 
 
 def test_router_hand_values_and_ties(ops):

@@ -11,12 +11,13 @@ import torch
 
 import cuttings
 import plain_qwen2_moe as plain
-from tiny_configs import TINY, pick_prompt
+from tiny_configs import TINY, prompt
 
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TOL = {"float32": 1e-4, "bfloat16": 1e-2}
+# positions whose routing is a near-tie for the precision under test are not compared (see test_engine_gpu.py)
 MARGIN = {"float32": 1e-6, "bfloat16": 2e-4}
 
 
@@ -65,8 +66,8 @@ def read_logits(out_dir, steps, vocab):
 def test_trace_run_mixed(name, dtype, tiny_folders, tmp_path):
     V = TINY[name]["cfg"]["vocab_size"]
     oracle = plain.PlainModel(tiny_folders[name], compute=torch.float64, emulate_bf16=(dtype == "bfloat16"))
-    reqs = {f"q{i}": pick_prompt(oracle, 200 + i, n, V, MARGIN[dtype]) for i, n in enumerate([70, 33, 100, 16, 90, 5])}
-    toks = {rid: t for rid, (t, _) in reqs.items()}
+    toks = {f"q{i}": prompt(200 + i, n, V) for i, n in enumerate([70, 33, 100, 16, 90, 5])}
+    margins = {rid: oracle.router_margins(t) for rid, t in toks.items()}
     steps, _ = cuttings.mixed(toks, max_live=4, seed=9)
     # some entries ask for nothing, some for a part
     for i, st in enumerate(steps):
@@ -80,13 +81,12 @@ def test_trace_run_mixed(name, dtype, tiny_folders, tmp_path):
     got = read_logits(out_dir, steps, V)
     assert got, "no logits were written"
     checked = 0
-    full = {rid: oracle.logits(t) for rid, (t, _) in reqs.items()}
+    full = {rid: oracle.logits(t) for rid, t in toks.items()}
     for (rid, p), row in got.items():
-        t, clear = reqs[rid]
-        if p >= clear:
+        if float(margins[rid][p]) < MARGIN[dtype]:
             continue
         ref = full[rid][p]
         d = float((row - ref).abs().max())
         assert d <= TOL[dtype], f"{rid} position {p}: {d:.3e}"
         checked += 1
-    assert checked > 0.25 * len(got)
+    assert checked > 0.5 * len(got)

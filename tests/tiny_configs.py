@@ -43,17 +43,3 @@ def prompt(seed, length, vocab):
     g = torch.Generator().manual_seed(1000 + seed)
     return torch.randint(0, vocab, (length,), generator=g).tolist()
 
-
-def pick_prompt(oracle, seed, length, vocab, min_margin, tries=8):
-    """Among the seeded prompts seed, seed + 1000, ... the one with the longest prefix on which
-    the oracle routes with a margin of at least ``min_margin`` (see PlainModel.router_margins).
-    Returns (tokens, length of that prefix)."""
-    best, best_clear = None, -1
-    for i in range(tries):
-        p = prompt(seed + 1000 * i, length, vocab)
-        c = oracle.clear_prefix(p, min_margin)
-        if c > best_clear:
-            best, best_clear = p, c
-        if c == length:
-            break
-    return best, best_clear
