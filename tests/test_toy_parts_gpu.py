@@ -1,0 +1,141 @@
+"""Parts defined outside the package can be registered, built and stepped without a change
+to the package's files: a mixer that keeps state of its own per request, and a whole toy
+architecture around it with its own config class.  The toy is not a model of anyone's."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def define_toy():
+    from dlm_b200.parts.base import Mixer, ParamSpec, PartSpec, RequestState
+    from dlm_b200.parts.model import ModelSpec
+    from dlm_b200.registry import register_architecture, register_part
+
+    class DecayingSumMixer(Mixer):
+        """y_t = W_out · s_t with s_t = decay * s_{t-1} + W_in · h_t: a linear recurrence whose state
+        s (one vector per request) lives in the request's state slot between steps.  A portion of
+        several tokens is scanned in order, so any cut of the sequence gives the same result."""
+
+        def __init__(self, hidden_size, state_size, decay):
+            self.hidden, self.n, self.decay = hidden_size, state_size, decay
+            self.w_in = self.w_out = None
+
+        def param_specs(self):
+            return [ParamSpec("in_proj.weight", (self.n, self.hidden)), ParamSpec("out_proj.weight", (self.hidden, self.n))]
+
+        def load(self, tensors, rt):
+            self.w_in, self.w_out = rt.matrix(tensors["in_proj.weight"]), rt.matrix(tensors["out_proj.weight"])
+
+        def state_need(self):
+            return RequestState((self.n,), torch.float32)
+
+        def forward(self, h, resid, ctx, call):
+            ops, b = ctx.rt.ops, ctx.batch
+            state = ctx.state(call)                                   # [slots, n]
+            u = ops.linear(h, self.w_in, None, torch.float32)         # [T, n]
+            cu, slots = b.cu_q.tolist(), b.state_slot.tolist()
+            s_all = torch.empty_like(u)
+            for r, slot in enumerate(slots):                          # a plain scan: this is a toy
+                s = state[slot]
+                for t in range(cu[r], cu[r + 1]):
+                    s = self.decay * s + u[t]
+                    s_all[t] = s
+                state[slot] = s
+            ops.linear_add(s_all.to(ctx.rt.dtype), self.w_out, resid)
+
+    @dataclass
+    class ToyConfig:
+        hidden_size: int
+        vocab_size: int
+        num_hidden_layers: int
+        state_size: int
+        decay: float
+        intermediate_size: int
+        rms_norm_eps: float = 1e-6
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+        def to_dict(self):
+            d = dict(self.__dict__)
+            d["architectures"] = ["ToyRecurrentLM"]
+            return d
+
+    def build_spec(cfg):
+        norm = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps})
+        layers, prefixes = [], []
+        for i in range(cfg.num_hidden_layers):
+            # odd layers mix with the toy recurrence, even layers with the package's attention
+            mixer = (PartSpec("toy_decaying_sum", {"hidden_size": cfg.hidden_size, "state_size": cfg.state_size,
+                                                   "decay": cfg.decay}) if i % 2 else
+                     PartSpec("gqa_attention", {"hidden_size": cfg.hidden_size, "num_heads": 2, "num_kv_heads": 1,
+                                                "head_dim": 16, "qkv_bias": False, "window": None,
+                                                "position": PartSpec("rope_neox", {"head_dim": 16, "theta": 1e4})}))
+            ffn = PartSpec("swiglu_dense", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
+            layers.append(PartSpec("prenorm", {"norm1": norm, "mixer": mixer, "norm2": norm, "ffn": ffn}))
+            prefixes.append(f"toy.layers.{i}.")
+        return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
+                         layer_prefixes=prefixes, final_norm=norm, final_norm_prefix="toy.norm.",
+                         embed_name="toy.embed.weight", lm_head_name="toy.head.weight")
+
+    register_part("mixer", "toy_decaying_sum", DecayingSumMixer)
+    register_architecture("ToyRecurrentLM", ToyConfig, build_spec)
+    return ToyConfig
+
+
+def plain_toy(folder, tokens):
+    """The toy model over a whole sequence in plain PyTorch (double precision)."""
+    import plain_qwen2_moe as plain
+    cfg, t = plain.load_folder(folder)
+    t = {k: v.double() for k, v in t.items()}
+    T = len(tokens)
+    x = t["toy.embed.weight"][torch.tensor(tokens)]
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"toy.layers.{i}."
+        n = plain.rmsnorm(x, t[p + "norm1.weight"], cfg["rms_norm_eps"])
+        if i % 2:
+            u = n @ t[p + "mixer.in_proj.weight"].T
+            s, rows = torch.zeros(cfg["state_size"], dtype=torch.float64), []
+            for j in range(T):
+                s = cfg["decay"] * s + u[j]
+                rows.append(s)
+            x = x + torch.stack(rows) @ t[p + "mixer.out_proj.weight"].T
+        else:
+            q, k, v = (n @ t[p + f"mixer.{c}_proj.weight"].T for c in "qkv")
+            pos, inv = torch.arange(T), plain.rope_inv_freqs(16, 1e4)
+            ctx = plain.attention(plain.rope(q.view(T, 2, 16), pos, inv), plain.rope(k.view(T, 1, 16), pos, inv),
+                                  v.view(T, 1, 16), None).reshape(T, 32)
+            x = x + ctx @ t[p + "mixer.o_proj.weight"].T
+        n2 = plain.rmsnorm(x, t[p + "norm2.weight"], cfg["rms_norm_eps"])
+        x = x + plain.swiglu_ffn(n2, t[p + "ffn.gate_proj.weight"], t[p + "ffn.up_proj.weight"],
+                                 t[p + "ffn.down_proj.weight"], lambda z: z)
+    return plain.rmsnorm(x, t["toy.norm.weight"], cfg["rms_norm_eps"]) @ t["toy.head.weight"].T
+
+
+def test_toy_mixer_with_state(tmp_path):
+    import cuttings
+    from dlm_b200.engine import Engine
+    from dlm_b200.weights import write_random_model
+    ToyConfig = define_toy()
+    cfg = ToyConfig(hidden_size=40, vocab_size=97, num_hidden_layers=4, state_size=24, decay=0.9, intermediate_size=56)
+    folder = write_random_model(cfg, 7, str(tmp_path / "toy"))
+    eng = Engine.from_pretrained(folder, dtype="float32", page_size=16, num_pages=24, max_requests=4)
+    assert len(eng.cache.state) == 2 and len(eng.cache.k) == 2 and not eng.use_graphs
+    g = torch.Generator().manual_seed(3)
+    reqs = {f"t{i}": torch.randint(0, 97, (n,), generator=g).tolist() for i, n in enumerate([45, 9, 70, 30, 18])}
+    ref = {rid: plain_toy(folder, toks) for rid, toks in reqs.items()}
+    mixed, _ = cuttings.mixed(reqs, max_live=3, seed=4)
+    for steps in (cuttings.whole(reqs), cuttings.portions(reqs), cuttings.tail_decode(reqs, 12), mixed):
+        got = cuttings.run_trace(eng, steps)
+        assert len(got) == sum(map(len, reqs.values()))
+        for (rid, p), row in got.items():
+            assert float((row.double() - ref[rid][p]).abs().max()) < 1e-4, (rid, p)
+    # a slot's state starts from zero for the next request that takes it
+    outs = eng.generate([reqs["t1"], reqs["t3"]], max_new_tokens=5)
+    assert outs == [eng.generate(reqs["t1"], max_new_tokens=5), eng.generate(reqs["t3"], max_new_tokens=5)]
+    for p, o in zip((reqs["t1"], reqs["t3"]), outs):
+        assert int(torch.argmax(plain_toy(folder, p)[-1])) == o[0]
