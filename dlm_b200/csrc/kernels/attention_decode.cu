@@ -350,3 +350,104 @@ void attention_decode(const void* q, const void* k_cache, const void* v_cache, c
 }
 
 }  // namespace dlmk
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (see no_alloc.h for its terms).  It launches the same
+// kernels as attention_decode above; only the home of the scratch differs.
+#include <cstdio>
+
+#include "no_alloc.h"
+
+namespace {
+
+// Partial results of the split-key kernel, and a status block whose first word the kernels set when
+// they refuse an access.  In host code this name is only a handle for cudaGetSymbolAddress; it is
+// not a device address and must never be passed to a kernel as one.
+static __device__ __align__(256) float g_noalloc_scratch[DLM_B200_NOALLOC_SCRATCH_FLOATS + 64];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+void noalloc_fail(char* msg, size_t len, const char* text) {
+    if (msg != nullptr && len > 0) snprintf(msg, len, "%s", text);
+}
+
+}  // namespace
+
+extern "C" int dlm_b200_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                                 const int32_t* block_table, int table_width, const int32_t* cu_q,
+                                                 const int32_t* kv_len, void* out, int R, int nh, int nkv, int hd,
+                                                 int page_size, int total_pages, int window, float scale,
+                                                 int max_kv_len, cudaStream_t stream, char* err_msg,
+                                                 size_t err_msg_len) {
+    using namespace dlmk;
+    if (err_msg != nullptr && err_msg_len > 0) err_msg[0] = '\0';
+    if (R <= 0) return 0;
+    if (!attention_decode_ok(hd) || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_kv_len < 1) {
+        noalloc_fail(err_msg, err_msg_len, "decode attention: head_dim must be a multiple of 8 in 16..256, heads a "
+                                           "multiple of kv heads, page_size and max_kv_len positive");
+        return 1;
+    }
+    int n_splits = 0, chunk = 0;
+    attention_decode_plan(R, nkv, max_kv_len, &n_splits, &chunk);
+    const size_t need = attention_decode_scratch_floats(R, nh, hd, n_splits);
+    if (need > (size_t)DLM_B200_NOALLOC_SCRATCH_FLOATS) {
+        char text[200];
+        snprintf(text, sizeof(text), "decode attention without allocation: %zu floats of partial results exceed the "
+                 "built-in maximum of %u (requests x heads x splits x (head_dim + 2))", need,
+                 (unsigned)DLM_B200_NOALLOC_SCRATCH_FLOATS);
+        noalloc_fail(err_msg, err_msg_len, text);
+        return 1;
+    }
+    // set-up, once per device, with that device current: the array's device address
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) {
+        noalloc_fail(err_msg, err_msg_len, "decode attention without allocation: device index out of range");
+        return 1;
+    }
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            noalloc_fail(err_msg, err_msg_len, "decode attention without allocation: cudaGetSymbolAddress failed");
+            return e != cudaSuccess ? (int)e : 1;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    float* scratch = g_noalloc_ptr[dev];
+    int* status = reinterpret_cast<int*>(scratch + DLM_B200_NOALLOC_SCRATCH_FLOATS);
+    e = cudaMemsetAsync(status, 0, sizeof(int), stream);      // the one word that must start at zero
+    if (e != cudaSuccess) return (int)e;
+
+    const int group = nh / nkv;
+    const int gt = group >= 8 ? 8 : (group > 2 ? (group > 4 ? 8 : 4) : group);
+    const int head_passes = (group + gt - 1) / gt;
+    int lpk = 1;
+    while (lpk * 8 < hd) lpk <<= 1;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)R * nh * n_splits * hd;
+    dim3 grid(R, nkv * head_passes, n_splits);
+    using T = __nv_bfloat16;
+#define DLM_NOALLOC_CASE(L)                                                                                      \
+    case L: launch_decode<T, L>(gt, grid, 0, stream, q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, \
+                                part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale, chunk,       \
+                                n_splits, head_passes, status); break;
+    switch (lpk) {
+        DLM_NOALLOC_CASE(2)
+        DLM_NOALLOC_CASE(4)
+        DLM_NOALLOC_CASE(8)
+        DLM_NOALLOC_CASE(16)
+        default: launch_decode<T, 32>(gt, grid, 0, stream, q, k_cache, v_cache, block_table, table_width, cu_q,
+                                      kv_len, part_o, part_ml, nh, nkv, hd, page_size, total_pages, window, scale,
+                                      chunk, n_splits, head_passes, status); break;
+    }
+#undef DLM_NOALLOC_CASE
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    attention_decode_merge_kernel<T><<<dim3(R, nh), 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<T*>(out), nh,
+                                                                      hd, n_splits);
+    e = cudaGetLastError();
+    return (int)e;
+}
