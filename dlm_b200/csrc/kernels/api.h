@@ -50,8 +50,9 @@ size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 // Router: logits = h · w^T (32-bit), softmax over E, top-k (ties: lower index), optional renormalisation.
 // has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).  norm_w != nullptr: h is the 32-bit residual and
 // rmsnorm(h, norm_w, eps) is applied first, in 32-bit (dtype is then the weights' dtype only).
-void router_topk(const void* h, const void* w, const float* norm_w, float eps, int32_t* ids, float* wts, float* gate,
-                 int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream);
+// logits: scratch of T * (E + has_gate) floats (the router logits are left there).
+void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
+                 float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream);
 
 // Groups the n = T * k (token, choice) pairs by expert: offsets[E + 1], rows[n] = token of each sorted row,
 // dest[n] = sorted row of pair (t, j).

@@ -21,8 +21,12 @@ void attention(const void* q, const void* k_cache, const void* v_cache, const in
     if (decode) {
         int n_splits, chunk;
         attention_decode_plan(R, nkv, max_kv_len < 1 ? 1 : max_kv_len, &n_splits, &chunk);
-        attention_decode(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, scratch, R, nh, nkv, hd,
-                         page_size, total_pages, window, scale, n_splits, chunk, dtype, stream);
+        if (dtype == BF16 && attention_prefill_ok(hd))
+            attention_decode_mma(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, scratch, R, nh, nkv,
+                                 hd, page_size, total_pages, window, scale, n_splits, chunk, stream);
+        else
+            attention_decode(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, scratch, R, nh, nkv, hd,
+                             page_size, total_pages, window, scale, n_splits, chunk, dtype, stream);
     }
     if (!decode || num_single < R) {
         if (fast && dtype == BF16 && attention_prefill_ok(hd))

@@ -351,6 +351,22 @@ void attention_decode(const void* q, const void* k_cache, const void* v_cache, c
 
 }  // namespace dlmk
 
+namespace dlmk {
+
+// The second stage alone (shared with the tensor-core decode kernel): merges the chunks' partial results.
+void attention_decode_merge(const float* part_o, const float* part_ml, const int32_t* cu_q, void* out, int R, int nh,
+                            int hd, int n_splits, int dtype, cudaStream_t stream) {
+    if (R <= 0) return;
+    dim3 mgrid(R, nh);
+    if (dtype == F32)
+        attention_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
+    else
+        attention_decode_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
+    check_launch("attention_decode_merge");
+}
+
+}  // namespace dlmk
+
 // ---------------------------------------------------------------------------------------------
 // The entry point that allocates nothing (see no_alloc.h for its terms).  It launches the same
 // kernels as attention_decode above; only the home of the scratch differs.

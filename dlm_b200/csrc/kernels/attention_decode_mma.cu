@@ -1,0 +1,290 @@
+// Decode attention on the warp-level tensor-core path (bfloat16): one query token per request,
+// the query heads of one kv head's group stacked as the rows of a 16-row MMA tile (rows beyond the
+// group are zero).  The arithmetic per byte of keys and values read drops to a few instructions,
+// which is what lets the kernel follow memory bandwidth; the FMA version in attention_decode.cu
+// spends its time on conversions and multiply-adds instead.
+//
+// One block = (request, kv head [x pass of 16 heads], chunk of keys).  Keys and values arrive in
+// tiles of 64 through asynchronous 16-byte copies, two tiles in flight; each of the 4 warps takes
+// 16 keys of a tile, keeps a running maximum / sum / output of its own, and the four are merged at
+// the end.  Partial results go to the same scratch layout as the FMA version; the merge kernel is
+// shared.
+#include "api.h"
+#include "attention_internal.h"
+#include "common.cuh"
+
+namespace dlmk {
+
+namespace {
+
+constexpr int WARPS = 4, BKV = 64, ROWS = 16;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                            const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
+                            int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
+                            float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int page_size,
+                            int page_shift, int total_pages, int window, float scale_log2, int chunk, int n_splits,
+                            int head_passes, int* err) {
+    constexpr int PITCH = HD + 8;
+    constexpr int KS = HD / 16, DT = HD / 8, CPR = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [ROWS][PITCH]
+    __nv_bfloat16* Ks = Qs + ROWS * PITCH;                               // [2][BKV][PITCH]
+    __nv_bfloat16* Vs = Ks + 2 * BKV * PITCH;                            // [2][BKV][PITCH]
+
+    const int r = blockIdx.x;
+    const int kvh = blockIdx.y / head_passes, pass = blockIdx.y % head_passes;
+    const int sp = blockIdx.z;
+    if (cu_q[r + 1] - cu_q[r] != 1) return;
+    const int group = nh / nkv;
+    const int h0 = kvh * group + pass * ROWS;
+    const int n_heads = min(ROWS, group - pass * ROWS);
+    const int len = kv_len[r], p = len - 1;
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int j_begin = max(lo, sp * chunk), j_end = min(len, (sp + 1) * chunk);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int token = cu_q[r];
+
+    float o[DT][4];
+#pragma unroll
+    for (int i = 0; i < DT; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    if (j_begin < j_end) {
+        const int32_t* table = block_table + (long long)r * table_width;
+        for (int idx = tid; idx < ROWS * CPR; idx += WARPS * 32) {
+            const int row = idx / CPR, c = idx % CPR;
+            if (row < n_heads) cp_async16(Qs + row * PITCH + c * 8, q + ((long long)token * nh + h0 + row) * HD + c * 8);
+            else *reinterpret_cast<uint4*>(Qs + row * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+
+        auto fill = [&](int stage, int j0) {
+            __nv_bfloat16* kd = Ks + (size_t)stage * BKV * PITCH;
+            __nv_bfloat16* vd = Vs + (size_t)stage * BKV * PITCH;
+            for (int idx = tid; idx < BKV * CPR; idx += WARPS * 32) {
+                const int key = idx / CPR, c = idx % CPR;         // CPR is a compile-time constant
+                const int j = j0 + key;
+                int page = -1, in_page = 0;
+                if (j >= j_begin && j < j_end) {
+                    const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+                    in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+                    page = lp < table_width ? table[lp] : -1;
+                    if (page < 0 || page >= total_pages) { *err = 3; page = -1; }
+                }
+                if (page >= 0) {
+                    const long long off = (((long long)page * nkv + kvh) * page_size + in_page) * HD + c * 8;
+                    cp_async16(kd + key * PITCH + c * 8, k_cache + off);
+                    cp_async16(vd + key * PITCH + c * 8, v_cache + off);
+                } else {
+                    *reinterpret_cast<uint4*>(kd + key * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vd + key * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+
+        const int t_begin = (j_begin / BKV) * BKV;
+        const int n_tiles = (j_end - t_begin + BKV - 1) / BKV;
+        fill(0, t_begin);
+        const int lm_row = lane & 15, lm_col = (lane >> 4) * 8;
+        uint32_t qf[KS][4];
+        for (int it = 0; it < n_tiles; ++it) {
+            const int stage = it & 1;
+            const int j0 = t_begin + it * BKV;
+            if (it + 1 < n_tiles) {
+                fill(stage ^ 1, j0 + BKV);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            if (it == 0) {
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk) ldsm_x4(qf[kk], Qs + lm_row * PITCH + kk * 16 + lm_col);
+            }
+            const __nv_bfloat16* kt = Ks + (size_t)stage * BKV * PITCH + (warp * 16) * PITCH;
+            const __nv_bfloat16* vt = Vs + (size_t)stage * BKV * PITCH + (warp * 16) * PITCH;
+            const int jw = j0 + warp * 16;                        // this warp's 16 keys
+            if (jw < j_end && jw + 16 > j_begin) {                // warp-uniform
+                float s[2][4];
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk) {
+                    uint32_t kf[4];
+                    ldsm_x4(kf, kt + lm_row * PITCH + kk * 16 + lm_col);
+                    mma16816(s[0], qf[kk], kf[0], kf[2]);
+                    mma16816(s[1], qf[kk], kf[1], kf[3]);
+                }
+                float mx_a = m_a, mx_b = m_b;
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int j = jw + n * 8 + 2 * t + (c & 1);
+                        const float v = (j >= j_begin && j < j_end) ? s[n][c] * scale_log2 : -INFINITY;
+                        s[n][c] = v;
+                        if (c < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
+                    }
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+                const float base_a = mx_a == -INFINITY ? 0.f : mx_a, base_b = mx_b == -INFINITY ? 0.f : mx_b;
+                const float al_a = exp2f(m_a - base_a), al_b = exp2f(m_b - base_b);
+                const float p00 = exp2f(s[0][0] - base_a), p01 = exp2f(s[0][1] - base_a);
+                const float p02 = exp2f(s[0][2] - base_b), p03 = exp2f(s[0][3] - base_b);
+                const float p10 = exp2f(s[1][0] - base_a), p11 = exp2f(s[1][1] - base_a);
+                const float p12 = exp2f(s[1][2] - base_b), p13 = exp2f(s[1][3] - base_b);
+                float sum_a = (p00 + p01) + (p10 + p11), sum_b = (p02 + p03) + (p12 + p13);
+                sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+                sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+                sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+                sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+                l_a = l_a * al_a + sum_a;
+                l_b = l_b * al_b + sum_b;
+                m_a = mx_a;
+                m_b = mx_b;
+                const uint32_t pf[4] = {pack_bf16(p00, p01), pack_bf16(p02, p03), pack_bf16(p10, p11),
+                                        pack_bf16(p12, p13)};
+#pragma unroll
+                for (int dn = 0; dn < HD / 16; ++dn) {
+                    uint32_t vf[4];
+                    ldsm_x4_trans(vf, vt + lm_row * PITCH + dn * 16 + lm_col);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        o[2 * dn][c] *= (c < 2) ? al_a : al_b;
+                        o[2 * dn + 1][c] *= (c < 2) ? al_a : al_b;
+                    }
+                    mma16816(o[2 * dn], pf, vf[0], vf[1]);
+                    mma16816(o[2 * dn + 1], pf, vf[2], vf[3]);
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // merge the four warps' streams; the tiles' shared memory is free now
+    float* sm_m = reinterpret_cast<float*>(smem_raw);             // [WARPS][ROWS]
+    float* sm_l = sm_m + WARPS * ROWS;                            // [WARPS][ROWS]
+    float* sm_o = sm_l + WARPS * ROWS;                            // [WARPS][ROWS][HD]
+    __syncthreads();
+    if (t == 0) {
+        sm_m[warp * ROWS + g] = m_a; sm_m[warp * ROWS + g + 8] = m_b;
+        sm_l[warp * ROWS + g] = l_a; sm_l[warp * ROWS + g + 8] = l_b;
+    }
+#pragma unroll
+    for (int i = 0; i < DT; ++i) {
+        const int d = i * 8 + 2 * t;
+        sm_o[(warp * ROWS + g) * HD + d] = o[i][0];
+        sm_o[(warp * ROWS + g) * HD + d + 1] = o[i][1];
+        sm_o[(warp * ROWS + g + 8) * HD + d] = o[i][2];
+        sm_o[(warp * ROWS + g + 8) * HD + d + 1] = o[i][3];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n_heads * HD; idx += WARPS * 32) {
+        const int row = idx / HD, d = idx % HD;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, sm_m[w * ROWS + row]);
+        float acc = 0.f, ls = 0.f;
+        if (mx != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float ms = sm_m[w * ROWS + row];
+                if (ms == -INFINITY) continue;
+                const float a = exp2f(ms - mx);
+                acc = fmaf(a, sm_o[(w * ROWS + row) * HD + d], acc);
+                ls = fmaf(a, sm_l[w * ROWS + row], ls);
+            }
+        }
+        const long long base = ((long long)r * nh + (h0 + row)) * n_splits + sp;
+        part_o[base * HD + d] = acc;
+        // the merge kernel works with natural-base maxima
+        if (d == 0) { part_ml[base * 2] = mx * 0.6931471805599453f; part_ml[base * 2 + 1] = ls; }
+    }
+}
+
+template <int HD>
+void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
+            const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, float* part_o,
+            float* part_ml, int nh, int nkv, int page_size, int total_pages, int window, float scale, int chunk,
+            int n_splits, int head_passes) {
+    size_t smem = (size_t)(ROWS + 4 * BKV) * (HD + 8) * sizeof(__nv_bfloat16);
+    const size_t merge = sizeof(float) * (size_t)(2 * WARPS * ROWS + WARPS * ROWS * HD);
+    if (merge > smem) smem = merge;
+    int shift = -1;
+    if ((page_size & (page_size - 1)) == 0) { shift = 0; while ((1 << shift) < page_size) ++shift; }
+    auto kern = attention_decode_mma_kernel<HD>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, WARPS * 32, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
+        static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv,
+        page_size, shift, total_pages, window, scale * 1.4426950408889634f, chunk, n_splits, head_passes,
+        error_flag_ptr());
+}
+
+}  // namespace
+
+void attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                          int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch,
+                          int R, int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale,
+                          int n_splits, int chunk, cudaStream_t stream) {
+    if (R <= 0) return;
+    DLM_CHECK(attention_prefill_ok(hd), "decode attention: this head_dim has no tensor-core kernel");
+    DLM_CHECK(nh % nkv == 0, "attention: heads must be a multiple of kv heads");
+    const int group = nh / nkv;
+    const int head_passes = (group + ROWS - 1) / ROWS;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)R * nh * n_splits * hd;
+    dim3 grid(R, nkv * head_passes, n_splits);
+#define DLM_DECODE(HD)                                                                                              \
+    launch<HD>(grid, stream, q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv, \
+               page_size, total_pages, window, scale, chunk, n_splits, head_passes)
+    switch (hd) {
+        case 16: DLM_DECODE(16); break;
+        case 32: DLM_DECODE(32); break;
+        case 48: DLM_DECODE(48); break;
+        case 64: DLM_DECODE(64); break;
+        case 96: DLM_DECODE(96); break;
+        default: DLM_DECODE(128); break;
+    }
+#undef DLM_DECODE
+    check_launch("attention_decode_mma");
+    attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, n_splits, BF16, stream);
+}
+
+}  // namespace dlmk

@@ -30,4 +30,12 @@ void attention_decode(const void* q, const void* k_cache, const void* v_cache, c
                       int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale, int n_splits,
                       int chunk, int dtype, cudaStream_t stream);
 
+void attention_decode_merge(const float* part_o, const float* part_ml, const int32_t* cu_q, void* out, int R, int nh,
+                            int hd, int n_splits, int dtype, cudaStream_t stream);
+// The same on the tensor-core path (bfloat16, head sizes of attention_prefill_ok); same scratch, same plan.
+void attention_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                          int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, float* scratch,
+                          int R, int nh, int nkv, int hd, int page_size, int total_pages, int window, float scale,
+                          int n_splits, int chunk, cudaStream_t stream);
+
 }  // namespace dlmk

@@ -49,7 +49,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
                          int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int R, int nh, int nkv, int page_size, int total_pages,
-                         int window, float scale_log2, int skip_single, int* err) {
+                         int page_shift, int window, float scale_log2, int skip_single, int* err) {
     constexpr int PITCH = HD + 8;              // elements per shared-memory row (16 bytes of padding)
     constexpr int KS = HD / 16;                // k16 steps over the head dimension
     constexpr int DT = HD / 8;                 // n8 tiles of the output
@@ -106,14 +106,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         for (int idx = tid; idx < BKV * CPR; idx += WARPS * 32) {
             const int key = idx / CPR, c = idx % CPR;
             const int j = j0 + key;
-            int page = -1;
+            int page = -1, in_page = 0;
             if (j >= lo && j <= hi) {
-                const int lp = j / page_size;
+                const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+                in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
                 page = lp < table_width ? table[lp] : -1;
                 if (page < 0 || page >= total_pages) { *err = 3; page = -1; }
             }
             if (page >= 0) {
-                const long long off = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * HD + c * 8;
+                const long long off = (((long long)page * nkv + kvh) * page_size + in_page) * HD + c * 8;
                 cp_async16(kd + key * PITCH + c * 8, k_cache + off);
                 cp_async16(vd + key * PITCH + c * 8, v_cache + off);
             } else {
@@ -248,12 +249,14 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
             const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int R,
             int nh, int nkv, int page_size, int total_pages, int window, float scale, int skip_single) {
     const size_t smem = (size_t)(BQ + 4 * BKV) * (HD + 8) * sizeof(__nv_bfloat16);
+    int shift = -1;
+    if ((page_size & (page_size - 1)) == 0) { shift = 0; while ((1 << shift) < page_size) ++shift; }
     auto kern = attention_prefill_kernel<HD>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<grid, WARPS * 32, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
-        static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, window,
+        static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, shift, window,
         scale * 1.4426950408889634f, skip_single, error_flag_ptr());
 }
 

@@ -51,10 +51,11 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     m.def("attention_scratch_floats", [](int R, int nh, int nkv, int hd, int max_kv_len) {
         return dlmk::attention_scratch_floats(R, nh, nkv, hd, max_kv_len);
     });
-    m.def("router_topk", [](u64 h, u64 w, u64 norm_w, float eps, u64 ids, u64 wts, u64 gate, int T, int H, int E,
-                            int k, int norm, int has_gate, int dtype, u64 stream) {
-        dlmk::router_topk(ptr<const void>(h), ptr<const void>(w), ptr<const float>(norm_w), eps, ptr<int32_t>(ids),
-                          ptr<float>(wts), ptr<float>(gate), T, H, E, k, norm, has_gate, dtype, st(stream));
+    m.def("router_topk", [](u64 h, u64 w, u64 norm_w, float eps, u64 logits, u64 ids, u64 wts, u64 gate, int T, int H,
+                            int E, int k, int norm, int has_gate, int dtype, u64 stream) {
+        dlmk::router_topk(ptr<const void>(h), ptr<const void>(w), ptr<const float>(norm_w), eps, ptr<float>(logits),
+                          ptr<int32_t>(ids), ptr<float>(wts), ptr<float>(gate), T, H, E, k, norm, has_gate, dtype,
+                          st(stream));
     });
     m.def("moe_permute", [](u64 ids, int n, int k, int E, u64 offsets, u64 rows, u64 dest, u64 stream) {
         dlmk::moe_permute(ptr<const int32_t>(ids), n, k, E, ptr<int32_t>(offsets), ptr<int32_t>(rows),

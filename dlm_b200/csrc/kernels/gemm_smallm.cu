@@ -24,7 +24,7 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int KB = 32;          // k per block
-constexpr int UNROLL = 4;
+constexpr int UNROLL = 8;
 
 struct SmallParams {
     const __nv_bfloat16* a; int lda; const int32_t* a_rows;

@@ -23,22 +23,22 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-// One block per token.  Each expert's logit is one warp's dot product summed in a fixed order
-// (lane l takes elements 8l..8l+7 of every 256, then a shuffle tree), so routing does not depend
-// on what else is in the batch.  VEC: rows are 16-byte aligned and H is a multiple of 8.
+// Router logits: blockIdx.x = token, blockIdx.y = a block of ROUTER_WARPS experts, one warp per
+// expert.  Each logit is one warp's dot product summed in a fixed order (lane l takes elements
+// 8l..8l+7 of every 256, then a shuffle tree), so routing does not depend on what else is in the
+// batch.  VEC: rows are 16-byte aligned and H is a multiple of 8.
 // With norm_w != nullptr the input is the 32-bit residual and the RMS norm (weight norm_w, eps)
 // is applied here, in 32-bit, so that the router never sees a rounded activation.
+constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
+
 template <typename TX, typename T, bool VEC>
 __global__ void __launch_bounds__(ROUTER_THREADS)
-router_topk_kernel(const TX* __restrict__ h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
-                   int32_t* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int H, int E, int k,
-                   int norm, int has_gate) {
+router_logits_kernel(const TX* __restrict__ h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
+                     float* __restrict__ logits, int H, int rows) {
     extern __shared__ float smem[];
     __shared__ float scratch[32];
     float* x = smem;            // [H]
-    float* prob = x + H;        // [E + 1]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nwarp = blockDim.x >> 5;
     float ss = 0.f;
     for (int i = tid; i < H; i += blockDim.x) {
         const float v = to_f32(h[(long long)t * H + i]);
@@ -51,29 +51,41 @@ router_topk_kernel(const TX* __restrict__ h, const T* __restrict__ w, const floa
         for (int i = tid; i < H; i += blockDim.x) x[i] = (x[i] * inv) * norm_w[i];
     }
     __syncthreads();
-    const int rows = E + (has_gate ? 1 : 0);
-    for (int e = warp; e < rows; e += nwarp) {
-        const T* wr = w + (long long)e * H;
-        float s = 0.f;
-        if (VEC) {
-            for (int i = lane * 8; i < H; i += 256) {
-                float wv[8];
-                load8(wr + i, wv);
-                const float4 xa = *reinterpret_cast<const float4*>(x + i), xb = *reinterpret_cast<const float4*>(x + i + 4);
-                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+    const int e = blockIdx.y * ROUTER_WARPS + warp;
+    if (e >= rows) return;
+    const T* wr = w + (long long)e * H;
+    float s = 0.f;
+    if (VEC) {
+#pragma unroll 4
+        for (int i = lane * 8; i < H; i += 256) {
+            float wv[8];
+            load8(wr + i, wv);
+            const float4 xa = *reinterpret_cast<const float4*>(x + i), xb = *reinterpret_cast<const float4*>(x + i + 4);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
-                for (int j = 0; j < 8; ++j) s = fmaf(xv[j], wv[j], s);
-            }
-        } else {
-            for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
+            for (int j = 0; j < 8; ++j) s = fmaf(xv[j], wv[j], s);
         }
-        s = warp_sum(s);
-        if (lane == 0) prob[e] = s;
+    } else {
+        for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
     }
-    __syncthreads();
-    if (warp != 0) return;
+    s = warp_sum(s);
+    if (lane == 0) logits[(long long)t * rows + e] = s;
+}
+
+// Softmax over the experts, top-k (ties: lower index), optional renormalisation, the shared expert's
+// sigmoid gate.  One warp per token.
+__global__ void __launch_bounds__(128)
+router_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ wts,
+                     float* __restrict__ gate, int T, int E, int k, int norm, int has_gate) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    const int rows = E + (has_gate ? 1 : 0);
+    float* prob = smem + warp * (E + 1);
+    for (int e = lane; e < rows; e += 32) prob[e] = logits[(long long)t * rows + e];
+    __syncwarp();
     if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-prob[E]));
-    // softmax over the E experts
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
     mx = warp_max(mx);
@@ -88,7 +100,6 @@ router_topk_kernel(const TX* __restrict__ h, const T* __restrict__ w, const floa
     if (sum > 0.f)
         for (int e = lane; e < E; e += 32) prob[e] = prob[e] / sum;
     __syncwarp();
-    // k rounds of arg-max; equal probabilities: the lower index wins
     float chosen_sum = 0.f;
     for (int j = 0; j < k; ++j) {
         float bv = -1.f;
@@ -156,27 +167,35 @@ moe_permute_kernel(const int32_t* __restrict__ ids, int n, int k, int E, int32_t
 
 }  // namespace
 
-void router_topk(const void* h, const void* w, const float* norm_w, float eps, int32_t* ids, float* wts, float* gate,
-                 int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream) {
+void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
+                 float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
-    const size_t smem = sizeof(float) * (size_t)(H + E + 1);
-    DLM_CHECK(smem <= 200 * 1024, "router: hidden_size + num_experts does not fit in shared memory");
+    const size_t smem = sizeof(float) * (size_t)H;
+    DLM_CHECK(smem <= 200 * 1024, "router: hidden_size does not fit in shared memory");
+    DLM_CHECK(E <= 8192, "router: more than 8192 experts");
+    const int rows = E + (has_gate ? 1 : 0);
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-#define DLM_ROUTER(TX, T, VEC)                                                                                \
+    dim3 grid(T, (rows + ROUTER_WARPS - 1) / ROUTER_WARPS);
+#define DLM_ROUTER(TX, TW, VEC)                                                                               \
     {                                                                                                         \
-        auto kern = router_topk_kernel<TX, T, VEC>;                                                           \
+        auto kern = router_logits_kernel<TX, TW, VEC>;                                                        \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
-        kern<<<T_, ROUTER_THREADS, smem, stream>>>(static_cast<const TX*>(h), static_cast<const T*>(w), norm_w, \
-                                                   eps, ids, wts, gate, H, E, k, norm, has_gate);             \
+        kern<<<grid, ROUTER_THREADS, smem, stream>>>(static_cast<const TX*>(h), static_cast<const TW*>(w),    \
+                                                     norm_w, eps, logits, H, rows);                           \
     }
-    const int T_ = T;
     // with norm_w the activations are the 32-bit residual whatever the weights' dtype
     if (dtype == F32) { if (vec) DLM_ROUTER(float, float, true) else DLM_ROUTER(float, float, false) }
     else if (norm_w != nullptr) { if (vec) DLM_ROUTER(float, __nv_bfloat16, true) else DLM_ROUTER(float, __nv_bfloat16, false) }
     else { if (vec) DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, false) }
 #undef DLM_ROUTER
-    check_launch("router_topk");
+    check_launch("router_logits");
+    const int wpb = 4;
+    const size_t smem2 = sizeof(float) * (size_t)wpb * (E + 1);
+    cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    router_select_kernel<<<(T + wpb - 1) / wpb, wpb * 32, smem2, stream>>>(logits, ids, wts, gate, T, E, k, norm,
+                                                                           has_gate);
+    check_launch("router_select");
 }
 
 void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int32_t* rows, int32_t* dest,

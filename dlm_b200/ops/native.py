@@ -149,9 +149,10 @@ class NativeOps:
         ids = torch.empty((T, k), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, k), dtype=torch.float32, device=h.device)
         gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
-        self.launches += 1
-        self.k.router_topk(_p(h), _p(w), _p(norm_weight), float(eps), _p(ids), _p(wts), _p(gate), T, H, E, k,
-                           int(norm), int(has_gate), _dt(w.dtype), self._stream())
+        logits = torch.empty((T, w.shape[0]), dtype=torch.float32, device=h.device)
+        self.launches += 2
+        self.k.router_topk(_p(h), _p(w), _p(norm_weight), float(eps), _p(logits), _p(ids), _p(wts), _p(gate), T, H,
+                           E, k, int(norm), int(has_gate), _dt(w.dtype), self._stream())
         return ids, wts, gate
 
     def moe_permute(self, ids, E):
