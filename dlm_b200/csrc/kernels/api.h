@@ -30,6 +30,15 @@ void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw,
           const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N, int K,
           int in_dtype, int out_dtype, int epilogue, int fast, cudaStream_t stream);
 
+// True when the tcgen05 / TMA matrix kernel can be used (it needs the driver's tensor-map encoder; the
+// environment variable DLM_B200_NO_TCGEN05=1 switches it off).
+bool gemm_tc_enabled();
+
+// out[i, :] = src[rows[i], :] for bfloat16 / float32 rows of `width` elements (width * element size a multiple
+// of 16 bytes): the gather that puts an expert's rows side by side before a grouped product.
+void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, int width, int dtype,
+                 cudaStream_t stream);
+
 // Rotates q and k heads of qkv[T, (nh + 2 nkv) * hd] (f32) by position * inv_freq (split-half pairs within the
 // first rotary_dim dims; inv_freq == nullptr: no rotation), writes q to q_out[T, nh * hd] and, where
 // slots != nullptr and slots[t] >= 0, k and v to the paged caches [pages, nkv, page_size, hd].

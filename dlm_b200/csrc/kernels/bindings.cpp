@@ -76,5 +76,10 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                      ptr<const int32_t>(top_k), ptr<const float>(u), ptr<const int32_t>(seen_offsets),
                      ptr<const int32_t>(seen_tokens), ptr<float>(scratch), st(stream));
     });
+    m.def("gemm_tc_enabled", &dlmk::gemm_tc_enabled);
+    m.def("gather_rows", [](u64 src, u64 rows, u64 out, int n_rows, int width, int dtype, u64 stream) {
+        dlmk::gather_rows(ptr<const void>(src), ptr<const int32_t>(rows), ptr<void>(out), n_rows, width, dtype,
+                          st(stream));
+    });
     m.def("take_error_flag", &dlmk::take_error_flag);
 }

@@ -126,6 +126,15 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
     (void)kv_base;
 }
 
+// ------------------------------------------------------------------ row gather
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ rows,
+                                   uint4* __restrict__ out, int chunks) {
+    const int r = blockIdx.x;
+    const uint4* s = src + (long long)rows[r] * chunks;
+    uint4* o = out + (long long)r * chunks;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) o[i] = s[i];
+}
+
 // ------------------------------------------------------------------ moe combine
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ dest,
                                    const float* __restrict__ wts, const float* __restrict__ shared,
@@ -187,6 +196,16 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
     check_launch("rope_kv_write");
+}
+
+void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, int width, int dtype,
+                 cudaStream_t stream) {
+    if (n_rows <= 0) return;
+    const int bytes = width * (dtype == F32 ? 4 : 2);
+    DLM_CHECK(bytes % 16 == 0, "gather_rows: a row must be a multiple of 16 bytes");
+    gather_rows_kernel<<<n_rows, 128, 0, stream>>>(static_cast<const uint4*>(src), rows, static_cast<uint4*>(out),
+                                                   bytes / 16);
+    check_launch("gather_rows");
 }
 
 void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,

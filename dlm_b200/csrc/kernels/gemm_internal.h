@@ -24,4 +24,13 @@ void gemm_mma(const void* a, int lda, const int32_t* a_rows, const void* w, int 
               const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
               int K, int out_dtype, int epilogue, cudaStream_t stream);
 
+// tcgen05 / TMA kernel for many rows of A (bfloat16 inputs, rows of A contiguous: no gather).  gemm_tc returns
+// false when the tensor maps cannot be made (the caller then takes another kernel).
+bool gemm_tc_enabled();
+bool gemm_tc_ok(const void* a, int lda, const void* w, int ldw, long long w_expert_stride, int M, int N, int K,
+                int in_dtype);
+bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expert_offsets, int num_experts,
+             const float* bias, void* out, int ldo, int M, int N, int K, int out_dtype, int epilogue,
+             cudaStream_t stream);
+
 }  // namespace dlmk

@@ -41,6 +41,7 @@ class NativeOps:
         self.k = load_kernels()
         self.fast = 1 if fast else 0
         self.launches = 0        # kernels launched through this object (for the benchmark's count)
+        self.tc = bool(self.k.gemm_tc_enabled()) if fast else False
 
     @staticmethod
     def _stream() -> int:
@@ -100,6 +101,15 @@ class NativeOps:
         E, N, K = w_gate_up.shape
         M = rows.numel()
         out = torch.empty((M, N // 2), dtype=a.dtype, device=a.device)
+        if (self.fast and self.tc and a.dtype == torch.bfloat16 and M > 16 * E and K % 8 == 0
+                and a.stride(0) == K):
+            # many rows per expert: put each expert's rows side by side, so that the TMA can fetch them as tiles
+            gathered = torch.empty((M, K), dtype=a.dtype, device=a.device)
+            self.launches += 1
+            self.k.gather_rows(_p(a), _p(rows), _p(gathered), M, K, _dt(a.dtype), self._stream())
+            self._gemm(gathered, w_gate_up, out, M, N, K, self.k.EPI_SWIGLU, offsets=offsets, num_experts=E,
+                       w_expert_stride=N * K)
+            return out
         self._gemm(a, w_gate_up, out, M, N, K, self.k.EPI_SWIGLU, a_rows=rows, offsets=offsets, num_experts=E,
                    w_expert_stride=N * K)
         return out
