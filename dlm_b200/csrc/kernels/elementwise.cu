@@ -66,20 +66,22 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 }
 
 // ------------------------------------------------------- rotary + cache write
-// blockIdx.x = token, blockIdx.y = slice of the token's work; threads run over (head, dim) of q and k heads,
-// then over the v elements.
+// blockIdx.x = token, blockIdx.y = slice of the token's work.  The rotation angles of a token depend on the
+// pair index only, so each block computes the rotary_dim / 2 sines and cosines once (in shared memory); then
+// threads run over (head, pair) of the q and k heads, over the unrotated dims, and over the v elements.
 template <typename T>
 __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
                                      const float* __restrict__ inv_freq, int rotary_dim,
                                      const int32_t* __restrict__ slots, T* __restrict__ q_out, T* __restrict__ k_cache,
                                      T* __restrict__ v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
                                      int* err) {
+    extern __shared__ float sc[];                  // [2][rotary_dim / 2]: sines, cosines
     const int t = blockIdx.x;
     const int Q = nh * hd, KV = nkv * hd;
     const float* row = qkv + (long long)t * (Q + 2 * KV);
     const float pos = (float)positions[t];
-    const int half = rotary_dim / 2;
-    long long kv_base = -1;   // element offset of (page, head 0, offset-in-page, 0)
+    const int half = inv_freq != nullptr ? rotary_dim / 2 : 0;
+    const int rd = 2 * half;                       // dims that are rotated
     int in_page = 0, page = -1;
     if (slots != nullptr) {
         const int s = slots[t];
@@ -92,29 +94,40 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
             }
         }
     }
-    // q heads and k heads: rotate
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        sc[i] = sn;
+        sc[half + i] = cs;
+    }
+    __syncthreads();
     const int rot_heads = nh + nkv;
     const int tpt = blockDim.x * gridDim.y, tid0 = blockIdx.y * blockDim.x + threadIdx.x;
-    for (int idx = tid0; idx < rot_heads * hd; idx += tpt) {
-        const int h = idx / hd, d = idx % hd;
-        const float* src = row + (long long)h * hd;    // q heads then k heads are contiguous in qkv
-        float val;
-        if (inv_freq != nullptr && d < rotary_dim) {
-            const int i = d < half ? d : d - half;
-            const float ang = pos * inv_freq[i];
-            float s, c;
-            sincosf(ang, &s, &c);
-            const float a = src[i], b = src[i + half];
-            val = d < half ? (a * c - b * s) : (a * s + b * c);
-        } else {
-            val = src[d];
-        }
+    // rotated pairs (i, i + half) of every q and k head
+    for (int idx = tid0; idx < rot_heads * half; idx += tpt) {
+        const int h = idx / half, i = idx % half;
+        const float* src = row + (long long)h * hd;          // q heads then k heads are contiguous in qkv
+        const float a = src[i], b = src[i + half];
+        const float sn = sc[i], cs = sc[half + i];
+        const float lo = a * cs - b * sn, hi = a * sn + b * cs;
         if (h < nh) {
-            q_out[(long long)t * Q + idx] = from_f32<T>(val);
+            T* o = q_out + (long long)t * Q + h * hd;
+            o[i] = from_f32<T>(lo);
+            o[i + half] = from_f32<T>(hi);
         } else if (page >= 0) {
-            const int kh = h - nh;
-            k_cache[(((long long)page * nkv + kh) * page_size + in_page) * hd + d] = from_f32<T>(val);
+            T* o = k_cache + (((long long)page * nkv + (h - nh)) * page_size + in_page) * hd;
+            o[i] = from_f32<T>(lo);
+            o[i + half] = from_f32<T>(hi);
         }
+    }
+    // dims from rotary_dim on pass through
+    const int rest = hd - rd;
+    for (int idx = tid0; idx < rot_heads * rest; idx += tpt) {
+        const int h = idx / rest, d = rd + idx % rest;
+        const float val = row[(long long)h * hd + d];
+        if (h < nh) q_out[(long long)t * Q + h * hd + d] = from_f32<T>(val);
+        else if (page >= 0)
+            k_cache[(((long long)page * nkv + (h - nh)) * page_size + in_page) * hd + d] = from_f32<T>(val);
     }
     if (page >= 0) {
         const float* vsrc = row + Q + KV;
@@ -123,7 +136,6 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
             v_cache[(((long long)page * nkv + kh) * page_size + in_page) * hd + d] = from_f32<T>(vsrc[idx]);
         }
     }
-    (void)kv_base;
 }
 
 // ------------------------------------------------------------------ row gather
@@ -187,12 +199,13 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
     int slices = (work + threads - 1) / threads;
     if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
     dim3 grid(T, slices);
+    const size_t smem = inv_freq != nullptr ? sizeof(float) * rotary_dim : 0;
     if (dtype == F32)
-        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+        rope_kv_write_kernel<float><<<grid, threads, smem, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), nh, nkv, hd,
             page_size, total_pages, err);
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
     check_launch("rope_kv_write");

@@ -1,22 +1,27 @@
-// C = A · W^T for many rows of A on the fifth-generation tensor cores (tcgen05), bfloat16 in,
-// 32-bit accumulation in tensor memory.
+// C = A · W^T on the fifth-generation tensor cores (tcgen05), bfloat16 in, 32-bit accumulation in
+// tensor memory, with the operands' roles swapped: 128 rows of W are the MMA's M, the rows of A (tokens)
+// its N.  N may be any multiple of 16 up to 256, so an expert that got 137 tokens costs one MMA tile of
+// N = 144 instead of two 128-row tiles, and a decode batch of 64 tokens fits as it is.
 //
-// One block computes one 128 x BN tile of C.  Six warps, three roles:
+// One block computes one (128 weight rows) x (up to 256 tokens) tile of C^T.  Six warps, three roles:
 //   warp 4 (one lane)   the producer: for every 64-wide slice of K it waits for a free stage and asks the
-//                       TMA unit for the A tile (128 x 64) and the W tile (BN x 64); the copies land in
+//                       TMA unit for the W tile (128 x 64) and the A tile (tokens x 64); the copies land in
 //                       shared memory in the 128-byte-swizzled, K-major layout the MMA reads, and complete
 //                       a transaction barrier;
 //   warp 5 (one lane)   the MMA issuer: waits for a stage, issues four tcgen05.mma (K = 16 each) that
-//                       accumulate into the tile's 128 lanes x BN columns of tensor memory, and commits:
-//                       the commit frees the stage when the MMAs have read it, and, after the last
-//                       slice, tells the epilogue that the accumulator is complete.  Warp 5 also
-//                       allocates and frees the tensor memory;
-//   warps 0-3           the epilogue: each warp reads its 32 lanes of the accumulator with tcgen05.ld
-//                       (one row of the tile per thread), applies the epilogue (bias / accumulate into
-//                       the residual / SwiGLU of neighbouring columns) and stores.
+//                       accumulate into 128 lanes x N columns of tensor memory, and commits: the commit
+//                       frees the stage when the MMAs have read it and, after the last slice, tells the
+//                       epilogue that the accumulator is complete.  Warp 5 also allocates and frees the
+//                       tensor memory;
+//   warps 0-3           the epilogue: each warp reads its 32 lanes of the accumulator with tcgen05.ld.
+//                       A thread holds one output column (weight row) for 32 tokens at a time, so for each
+//                       token the warp stores 32 consecutive columns: coalesced without staging.  Bias,
+//                       accumulation into the residual, or SwiGLU (gate and up are neighbouring lanes).
+// The kernel is persistent: a block walks a strided list of tiles, and two accumulators alternate in tensor
+// memory, so that the epilogue of one tile overlaps the MMAs of the next.
 //
-// Dense, or grouped by expert (rows of one expert are consecutive; the tile list is walked as in the
-// other GEMM kernels).  Rows of A must be contiguous in memory (no gather): the caller gathers first.
+// Dense, or grouped by expert (rows of one expert are consecutive).  Rows of A must be contiguous in
+// memory (no gather): the caller gathers first.
 //
 // Every wait on a barrier is bounded.  If a bound is reached the block sets the error flag, stops
 // issuing work, gives in-flight copies time to land, frees its tensor memory and returns; the host
@@ -116,59 +121,71 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN, int STAGES, int EPI, typename TOut>
+constexpr int TT = 256;          // most tokens per tile (the MMA's N)
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct TileInfo { int expert, row_begin, row_end; };
+
+// Token tile `ty` of the launch: dense, rows [ty * TT, ...); grouped, the ty-th tile when every expert's rows
+// are cut into tiles of TT.  expert < 0: there is no such tile.
+__device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty) {
+    TileInfo t{0, ty * TT, p.M};
+    if (p.expert_offsets != nullptr) {
+        t.expert = -1;
+        int acc = 0;
+        for (int e = 0; e < p.num_experts; ++e) {
+            const int r0 = p.expert_offsets[e], r1 = p.expert_offsets[e + 1];
+            const int tiles_e = (r1 - r0 + TT - 1) / TT;
+            if (ty < acc + tiles_e) {
+                t.expert = e;
+                t.row_begin = r0 + (ty - acc) * TT;
+                t.row_end = r1;
+                break;
+            }
+            acc += tiles_e;
+        }
+    }
+    t.row_end = min(min(t.row_end, t.row_begin + TT), p.M);
+    if (t.row_begin >= t.row_end) t.expert = -1;
+    return t;
+}
+
+// Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulators in tensor memory
+// alternate, so that the epilogue of one tile runs while the MMAs of the next are issued.
+template <int STAGES, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, TcParams p) {
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    // M = 128, N = BN, bfloat16 x bfloat16 -> float32, both operands K-major
-    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a64,
+               const __grid_constant__ CUtensorMap map_a128, const __grid_constant__ CUtensorMap map_a256,
+               TcParams p, int nx, int total_tiles) {
+    constexpr uint32_t W_BYTES = BM * BK * 2, A_MAX_BYTES = TT * BK * 2, STAGE_BYTES = W_BYTES + A_MAX_BYTES;
+    // M = 128, bfloat16 x bfloat16 -> float32, both operands K-major; N is filled in per tile
+    constexpr uint32_t IDESC0 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
-    __shared__ __align__(8) uint64_t acc_bar;
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_tile[3];
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t raw_addr = smem_u32(smem_raw);
     unsigned char* tiles = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+    float* stg = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES);     // [32][65], SwiGLU staging
 
     if (tid == 0) {
         s_abort = 0;
-        s_tile[0] = 0;
-        if (p.expert_offsets != nullptr) {
-            int acc = 0;
-            s_tile[0] = -1;
-            for (int e = 0; e < p.num_experts; ++e) {
-                const int r0 = p.expert_offsets[e], r1 = p.expert_offsets[e + 1];
-                const int tiles_e = (r1 - r0 + BM - 1) / BM;
-                if ((int)blockIdx.y < acc + tiles_e) {
-                    s_tile[0] = e;
-                    s_tile[1] = r0 + ((int)blockIdx.y - acc) * BM;
-                    s_tile[2] = r1;
-                    break;
-                }
-                acc += tiles_e;
-            }
-        } else {
-            s_tile[1] = blockIdx.y * BM;
-            s_tile[2] = p.M;
-        }
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&acc_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
-    const int expert = s_tile[0];
-    const int row_begin = s_tile[1];
-    const int row_end = min(min(s_tile[2], row_begin + BM), p.M);
-    if (expert < 0 || row_begin >= row_end) return;           // uniform over the block; nothing allocated yet
-
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
-                     "r"((uint32_t)BN) : "memory");
+                     "r"((uint32_t)(2 * TT)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -176,70 +193,129 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     volatile int* abort_flag = &s_abort;
-
-    const int n0 = blockIdx.x * BN;
     const int k_tiles = (p.K + BK - 1) / BK;
 
     if (warp == 4) {
         if (lane == 0) {
-            const int w_row = (p.expert_offsets != nullptr ? expert * p.N : 0) + n0;
-            for (int kt = 0; kt < k_tiles; ++kt) {
-                const int s = kt % STAGES;
-                if (kt >= STAGES && !mbar_wait(&empty_bar[s], ((kt / STAGES) & 1) ^ 1, abort_flag)) break;
-                unsigned char* a_dst = tiles + (size_t)s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kt * BK, row_begin, &full_bar[s]);
-                tma_load_2d(a_dst + A_BYTES, &map_w, kt * BK, w_row, &full_bar[s]);
+            uint32_t it = 0;                                  // slices issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileInfo ti = tile_info(p, tile / nx);
+                if (ti.expert < 0) continue;
+                const int n0 = (tile % nx) * BM;
+                const int n_tok = ti.row_end - ti.row_begin;
+                const int box = n_tok <= 64 ? 64 : (n_tok <= 128 ? 128 : 256);
+                const CUtensorMap* map_a = box == 64 ? &map_a64 : (box == 128 ? &map_a128 : &map_a256);
+                const uint32_t tx = W_BYTES + (uint32_t)box * BK * 2;
+                const int w_row = (p.expert_offsets != nullptr ? ti.expert * p.N : 0) + n0;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    unsigned char* w_dst = tiles + (size_t)s * STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], tx);
+                    tma_load_2d(w_dst, &map_w, kt * BK, w_row, &full_bar[s]);
+                    tma_load_2d(w_dst + W_BYTES, map_a, kt * BK, ti.row_begin, &full_bar[s]);
+                }
             }
         }
     } else if (warp == 5) {
         if (lane == 0) {
+            uint32_t it = 0, acc_i = 0;
             bool ok = true;
-            for (int kt = 0; kt < k_tiles && ok; ++kt) {
-                const int s = kt % STAGES;
-                ok = mbar_wait(&full_bar[s], (kt / STAGES) & 1, abort_flag);
-                if (!ok) break;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const TileInfo ti = tile_info(p, tile / nx);
+                if (ti.expert < 0) continue;
+                const int n_mma = max(16, (ti.row_end - ti.row_begin + 15) & ~15);
+                const uint32_t idesc = IDESC0 | ((uint32_t)(n_mma >> 3) << 17);
+                const uint32_t b = acc_i & 1, u = acc_i >> 1;
+                // the epilogue must have drained this accumulator's previous tile
+                if (u >= 1 && !mbar_wait(&acc_empty[b], (u & 1) ^ 1, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+                const uint32_t d_tmem = tmem_base + b * TT;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t w_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t dw = umma_desc(w_addr), da = umma_desc(w_addr + W_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)          // 16 elements of K = 32 bytes = 2 address units
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, IDESC, (kt > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty_bar[s]);                // the stage is free once these MMAs have read it
+                    for (int k = 0; k < BK / 16; ++k)      // 16 elements of K = 32 bytes = 2 address units
+                        umma_bf16(d_tmem, dw + 2 * k, da + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);            // the stage is free once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[b]);                 // the accumulator is complete once all MMAs are done
+                ++acc_i;
             }
-            if (ok) umma_commit(&acc_bar);                 // the accumulator is complete once all MMAs are done
         }
     } else {
-        // epilogue: thread = one row of the tile; warp w may read tensor-memory lanes 32w .. 32w + 31
-        if (mbar_wait(&acc_bar, 0, abort_flag)) {
+        // epilogue: warp w reads tensor-memory lanes 32w .. 32w + 31 = output columns n0 + 32w + lane;
+        // the accumulator's columns are the tile's tokens
+        uint32_t acc_i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            TileInfo ti;
+            if (lane == 0) ti = tile_info(p, tile / nx);
+            ti.expert = __shfl_sync(0xffffffffu, ti.expert, 0);
+            ti.row_begin = __shfl_sync(0xffffffffu, ti.row_begin, 0);
+            ti.row_end = __shfl_sync(0xffffffffu, ti.row_end, 0);
+            if (ti.expert < 0) continue;
+            const int n0 = (tile % nx) * BM;
+            const int row_begin = ti.row_begin, row_end = ti.row_end;
+            const int n_mma = max(16, (row_end - row_begin + 15) & ~15);
+            const uint32_t b = acc_i & 1, u = acc_i >> 1;
+            if (!mbar_wait(&acc_full[b], u & 1, abort_flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = row_begin + warp * 32 + lane;
-            const bool row_ok = row < row_end;
+            const uint32_t d_tmem = tmem_base + b * TT + ((uint32_t)(warp * 32) << 16);
+            const int col = n0 + warp * 32 + lane;
+            const bool col_ok = col < p.N;
+            const float bias = (EPI == EPI_STORE && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < n_mma; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-                if (!row_ok) continue;
-                const int col0 = n0 + c0;
+                tmem_ld32(d_tmem + (uint32_t)c0, v);
+                const int tok0 = row_begin + c0;
                 if (EPI == EPI_SWIGLU) {
-                    TOut* o = static_cast<TOut*>(p.out) + (long long)row * p.ldo + (col0 >> 1);
+                    // even lanes hold gate, their odd neighbours up.  The products of the four warps are
+                    // gathered in shared memory as [32 tokens][64 outputs], so that a token's 64 outputs
+                    // leave as one contiguous run.
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2)
-                        if (col0 + j + 1 < p.N)
-                            o[j >> 1] = from_f32<TOut>(silu_f(__uint_as_float(v[j])) * __uint_as_float(v[j + 1]));
+                    for (int j = 0; j < 32; ++j) {
+                        const float mine = __uint_as_float(v[j]);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                        // the result is rounded to bfloat16: the fast exponential and division are exact enough
+                        if (!(lane & 1))
+                            stg[j * 65 + ((warp * 32 + lane) >> 1)] = __fdividef(mine, 1.0f + __expf(-mine)) * other;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    for (int idx = tid; idx < 32 * 64; idx += 128) {
+                        const int j = idx >> 6, c = idx & 63;
+                        if (tok0 + j < row_end && n0 + 2 * c + 1 < p.N)
+                            static_cast<TOut*>(p.out)[(long long)(tok0 + j) * p.ldo + (n0 >> 1) + c] =
+                                from_f32<TOut>(stg[j * 65 + c]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
                 } else if (EPI == EPI_ADD) {
-                    float* o = static_cast<float*>(p.out) + (long long)row * p.ldo + col0;
+                    float* o = static_cast<float*>(p.out) + (long long)tok0 * p.ldo + col;
+                    float old[32];                              // all of the chunk's residual loads in flight
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) o[j] += __uint_as_float(v[j]);
+                    for (int i = 0; i < 32; ++i)
+                        old[i] = (col_ok && tok0 + i < row_end) ? o[(long long)i * p.ldo] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col_ok && tok0 + i < row_end) o[(long long)i * p.ldo] = old[i] + __uint_as_float(v[i]);
                 } else {
-                    TOut* o = static_cast<TOut*>(p.out) + (long long)row * p.ldo + col0;
+                    TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + col;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N)
-                            o[j] = from_f32<TOut>(__uint_as_float(v[j]) + (p.bias ? p.bias[col0 + j] : 0.f));
+                        if (col_ok && tok0 + j < row_end)
+                            o[(long long)j * p.ldo] = from_f32<TOut>(__uint_as_float(v[j]) + bias);
                 }
             }
+            // this accumulator may be written again
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&acc_empty[b]);
+            ++acc_i;
         }
     }
 
@@ -253,7 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncthreads();
     }
     if (warp == 5) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * TT))
                      : "memory");
     }
 }
@@ -291,13 +367,25 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, int K, int ld,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 132;
+    }
+    return n;
+}
+
 template <int EPI, typename TOut>
-void launch(const CUtensorMap& ma, const CUtensorMap& mw, const TcParams& p, dim3 grid, cudaStream_t stream) {
-    constexpr int BN = 128, STAGES = 5;
-    const size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
-    auto kern = gemm_tc_kernel<BN, STAGES, EPI, TOut>;
+void launch(const CUtensorMap& mw, const CUtensorMap& m64, const CUtensorMap& m128, const CUtensorMap& m256,
+            const TcParams& p, int nx, int total_tiles, cudaStream_t stream) {
+    constexpr int STAGES = 4;
+    const size_t smem = (size_t)STAGES * (BM * BK * 2 + TT * BK * 2) + 32 * 65 * sizeof(float) + 1024;
+    auto kern = gemm_tc_kernel<STAGES, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, THREADS, smem, stream>>>(ma, mw, p);
+    const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
+    kern<<<grid, THREADS, smem, stream>>>(mw, m64, m128, m256, p, nx, total_tiles);
 }
 
 }  // namespace
@@ -326,20 +414,24 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
     DLM_CHECK(bias == nullptr || epilogue == EPI_STORE, "gemm: a bias goes with the store epilogue only");
-    constexpr int BN = 128;
-    CUtensorMap ma, mw;
+    CUtensorMap mw, m64, m128, m256;
     const long long w_rows = expert_offsets ? (long long)num_experts * N : N;
-    if (!make_map(&ma, a, M, K, lda, BM) || !make_map(&mw, w, w_rows, K, ldw, BN)) return false;
+    if (!make_map(&mw, w, w_rows, K, ldw, BM) || !make_map(&m64, a, M, K, lda, 64) ||
+        !make_map(&m128, a, M, K, lda, 128) || !make_map(&m256, a, M, K, lda, 256))
+        return false;
     TcParams p{expert_offsets, num_experts, bias, out, ldo, M, N, K, error_flag_ptr()};
-    int m_tiles = (M + BM - 1) / BM;
-    if (expert_offsets != nullptr) m_tiles += num_experts;
-    DLM_CHECK(m_tiles <= 65535, "gemm: too many row tiles for one launch");
-    dim3 grid((N + BN - 1) / BN, m_tiles);
+    int t_tiles = (M + TT - 1) / TT;
+    if (expert_offsets != nullptr) t_tiles += num_experts;
+    const int nx = (N + BM - 1) / BM;
+    DLM_CHECK((long long)nx * t_tiles < (1LL << 30), "gemm: too many tiles for one launch");
+    const int total_tiles = nx * t_tiles;
     const bool f32 = out_dtype == F32;
     switch (epilogue) {
-        case EPI_STORE: if (f32) launch<EPI_STORE, float>(ma, mw, p, grid, stream); else launch<EPI_STORE, __nv_bfloat16>(ma, mw, p, grid, stream); break;
-        case EPI_ADD: launch<EPI_ADD, float>(ma, mw, p, grid, stream); break;
-        default: if (f32) launch<EPI_SWIGLU, float>(ma, mw, p, grid, stream); else launch<EPI_SWIGLU, __nv_bfloat16>(ma, mw, p, grid, stream); break;
+        case EPI_STORE: if (f32) launch<EPI_STORE, float>(mw, m64, m128, m256, p, nx, total_tiles, stream);
+                        else launch<EPI_STORE, __nv_bfloat16>(mw, m64, m128, m256, p, nx, total_tiles, stream); break;
+        case EPI_ADD: launch<EPI_ADD, float>(mw, m64, m128, m256, p, nx, total_tiles, stream); break;
+        default: if (f32) launch<EPI_SWIGLU, float>(mw, m64, m128, m256, p, nx, total_tiles, stream);
+                 else launch<EPI_SWIGLU, __nv_bfloat16>(mw, m64, m128, m256, p, nx, total_tiles, stream); break;
     }
     check_launch("gemm_tc");
     return true;

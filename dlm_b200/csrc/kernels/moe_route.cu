@@ -72,6 +72,76 @@ router_logits_kernel(const TX* __restrict__ h, const T* __restrict__ w, const fl
     if (lane == 0) logits[(long long)t * rows + e] = s;
 }
 
+// The same for many tokens: a block takes ROUTER_TB tokens, so that a weight row read from memory meets all
+// of them.  Per token the sums run in exactly the order of router_logits_kernel, so a token's logits do not
+// depend on which of the two kernels computed them.
+constexpr int ROUTER_TB = 8;
+
+constexpr int ROUTER_EW = 4;     // experts per warp in the many-token kernel
+
+template <typename TX, typename T>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_logits_multi_kernel(const TX* __restrict__ h, const T* __restrict__ w, const float* __restrict__ norm_w,
+                           float eps, float* __restrict__ logits, int T_, int H, int rows) {
+    extern __shared__ float smem[];               // [ROUTER_TB][H]
+    __shared__ float scratch[32];
+    const int t0 = blockIdx.x * ROUTER_TB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nt = min(ROUTER_TB, T_ - t0);
+    for (int j = 0; j < ROUTER_TB; ++j) {
+        float* x = smem + (size_t)j * H;
+        if (j >= nt) {
+            for (int i = tid; i < H; i += blockDim.x) x[i] = 0.f;
+            continue;
+        }
+        float ss = 0.f;
+        for (int i = tid; i < H; i += blockDim.x) {
+            const float v = to_f32(h[(long long)(t0 + j) * H + i]);
+            x[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (norm_w != nullptr) {
+            ss = block_sum(ss, scratch);
+            const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+            for (int i = tid; i < H; i += blockDim.x) x[i] = (x[i] * inv) * norm_w[i];
+        }
+    }
+    __syncthreads();
+    // a warp takes ROUTER_EW experts x ROUTER_TB tokens: every activation read from shared memory meets
+    // ROUTER_EW weight rows, every weight meets ROUTER_TB tokens
+    const int e0 = (blockIdx.y * ROUTER_WARPS + warp) * ROUTER_EW;
+    if (e0 >= rows) return;
+    float s[ROUTER_EW][ROUTER_TB];
+#pragma unroll
+    for (int a = 0; a < ROUTER_EW; ++a)
+#pragma unroll
+        for (int j = 0; j < ROUTER_TB; ++j) s[a][j] = 0.f;
+    for (int i = lane * 8; i < H; i += 256) {
+        float wv[ROUTER_EW][8];
+#pragma unroll
+        for (int a = 0; a < ROUTER_EW; ++a) {
+            const int e = min(e0 + a, rows - 1);            // rows beyond the table repeat the last one (not stored)
+            load8(w + (long long)e * H + i, wv[a]);
+        }
+#pragma unroll
+        for (int j = 0; j < ROUTER_TB; ++j) {
+            const float* x = smem + (size_t)j * H + i;
+            const float4 xa = *reinterpret_cast<const float4*>(x), xb = *reinterpret_cast<const float4*>(x + 4);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int a = 0; a < ROUTER_EW; ++a)
+#pragma unroll
+                for (int q = 0; q < 8; ++q) s[a][j] = fmaf(xv[q], wv[a][q], s[a][j]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < ROUTER_EW; ++a)
+#pragma unroll
+        for (int j = 0; j < ROUTER_TB; ++j) {
+            const float v = warp_sum(s[a][j]);
+            if (lane == 0 && j < nt && e0 + a < rows) logits[(long long)(t0 + j) * rows + e0 + a] = v;
+        }
+}
+
 // Softmax over the experts, top-k (ties: lower index), optional renormalisation, the shared expert's
 // sigmoid gate.  One warp per token.
 __global__ void __launch_bounds__(128)
@@ -176,6 +246,23 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     DLM_CHECK(E <= 8192, "router: more than 8192 experts");
     const int rows = E + (has_gate ? 1 : 0);
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    const size_t smem_multi = sizeof(float) * (size_t)H * ROUTER_TB;
+    if (vec && T >= 32 && smem_multi <= 200 * 1024) {
+        dim3 mgrid((T + ROUTER_TB - 1) / ROUTER_TB,
+                   (rows + ROUTER_WARPS * ROUTER_EW - 1) / (ROUTER_WARPS * ROUTER_EW));
+#define DLM_ROUTER_MULTI(TX, TW)                                                                              \
+    {                                                                                                         \
+        auto kern = router_logits_multi_kernel<TX, TW>;                                                       \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_multi);             \
+        kern<<<mgrid, ROUTER_THREADS, smem_multi, stream>>>(static_cast<const TX*>(h), static_cast<const TW*>(w), \
+                                                            norm_w, eps, logits, T, H, rows);                 \
+    }
+        if (dtype == F32) DLM_ROUTER_MULTI(float, float)
+        else if (norm_w != nullptr) DLM_ROUTER_MULTI(float, __nv_bfloat16)
+        else DLM_ROUTER_MULTI(__nv_bfloat16, __nv_bfloat16)
+#undef DLM_ROUTER_MULTI
+        check_launch("router_logits_multi");
+    } else {
     dim3 grid(T, (rows + ROUTER_WARPS - 1) / ROUTER_WARPS);
 #define DLM_ROUTER(TX, TW, VEC)                                                                               \
     {                                                                                                         \
@@ -190,6 +277,7 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     else { if (vec) DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, false) }
 #undef DLM_ROUTER
     check_launch("router_logits");
+    }
     const int wpb = 4;
     const size_t smem2 = sizeof(float) * (size_t)wpb * (E + 1);
     cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
