@@ -3,17 +3,17 @@
 // its N.  N may be any multiple of 16 up to 256, so an expert that got 137 tokens costs one MMA tile of
 // N = 144 instead of two 128-row tiles, and a decode batch of 64 tokens fits as it is.
 //
-// One block computes one (128 weight rows) x (up to 256 tokens) tile of C^T.  Six warps, three roles:
-//   warp 4 (one lane)   the producer: for every 64-wide slice of K it waits for a free stage and asks the
+// A tile of C^T is (128 weight rows) x (up to 256 tokens).  Ten warps, three roles:
+//   warp 8 (one lane)   the producer: for every 64-wide slice of K it waits for a free stage and asks the
 //                       TMA unit for the W tile (128 x 64) and the A tile (tokens x 64); the copies land in
 //                       shared memory in the 128-byte-swizzled, K-major layout the MMA reads, and complete
 //                       a transaction barrier;
-//   warp 5 (one lane)   the MMA issuer: waits for a stage, issues four tcgen05.mma (K = 16 each) that
+//   warp 9 (one lane)   the MMA issuer: waits for a stage, issues four tcgen05.mma (K = 16 each) that
 //                       accumulate into 128 lanes x N columns of tensor memory, and commits: the commit
 //                       frees the stage when the MMAs have read it and, after the last slice, tells the
-//                       epilogue that the accumulator is complete.  Warp 5 also allocates and frees the
+//                       epilogue that the accumulator is complete.  Warp 9 also allocates and frees the
 //                       tensor memory;
-//   warps 0-3           the epilogue: each warp reads its 32 lanes of the accumulator with tcgen05.ld.
+//   warps 0-7           the epilogue: each warp reads 32 lanes of the accumulator with tcgen05.ld.
 //                       A thread holds one output column (weight row) for 32 tokens at a time, so for each
 //                       token the warp stores 32 consecutive columns: coalesced without staging.  Bias,
 //                       accumulation into the residual, or SwiGLU (gate and up are neighbouring lanes).
@@ -38,7 +38,8 @@ namespace dlmk {
 
 namespace {
 
-constexpr int BM = 128, BK = 64, THREADS = 192;
+constexpr int BM = 128, BK = 64;
+constexpr int EPI_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, THREADS = 320;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;       // try_wait calls before a wait gives up
 
 struct TcParams {
@@ -123,6 +124,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 constexpr int TT = 256;          // most tokens per tile (the MMA's N)
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -175,15 +180,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t raw_addr = smem_u32(smem_raw);
     unsigned char* tiles = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-    float* stg = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES);     // [32][65], SwiGLU staging
 
     if (tid == 0) {
         s_abort = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPI_WARPS * 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                      "r"((uint32_t)(2 * TT)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -195,7 +199,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = &s_abort;
     const int k_tiles = (p.K + BK - 1) / BK;
 
-    if (warp == 4) {
+    if (warp == PRODUCER_WARP) {
         if (lane == 0) {
             uint32_t it = 0;                                  // slices issued so far, over all tiles
             bool ok = true;
@@ -218,7 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         if (lane == 0) {
             uint32_t it = 0, acc_i = 0;
             bool ok = true;
@@ -249,8 +253,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     } else {
-        // epilogue: warp w reads tensor-memory lanes 32w .. 32w + 31 = output columns n0 + 32w + lane;
-        // the accumulator's columns are the tile's tokens
+        // epilogue, eight warps: warp w reads tensor-memory lanes 32q .. 32q + 31 (q = w % 4) = output columns
+        // n0 + 32q + lane; the accumulator's columns are the tile's tokens, and the two warps of a quadrant
+        // take alternate chunks of 32 tokens.  A thread gets one output column for 32 tokens; the chunk is
+        // turned through the warp's own staging area so that it leaves as 16-byte stores along the rows.
+        const int q = warp & 3, hsel = warp >> 2;
+        float* st = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES) + warp * (32 * 33);
+        const bool vec_ok = (p.ldo % 8 == 0) && (p.N % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
         uint32_t acc_i = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -266,50 +275,120 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t b = acc_i & 1, u = acc_i >> 1;
             if (!mbar_wait(&acc_full[b], u & 1, abort_flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t d_tmem = tmem_base + b * TT + ((uint32_t)(warp * 32) << 16);
-            const int col = n0 + warp * 32 + lane;
+            const uint32_t d_tmem = tmem_base + b * TT + ((uint32_t)(q * 32) << 16);
+            const int colw = n0 + q * 32;                        // first output column of this warp
+            const int col = colw + lane;
             const bool col_ok = col < p.N;
             const float bias = (EPI == EPI_STORE && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < n_mma; c0 += 32) {
+            for (int c0 = hsel * 32; c0 < n_mma; c0 += 64) {
                 uint32_t v[32];
                 tmem_ld32(d_tmem + (uint32_t)c0, v);
                 const int tok0 = row_begin + c0;
+                const int n_valid = min(32, row_end - tok0);      // tokens of this chunk that exist
+                if (n_valid <= 0) continue;                       // uniform over the warp
                 if (EPI == EPI_SWIGLU) {
-                    // even lanes hold gate, their odd neighbours up.  The products of the four warps are
-                    // gathered in shared memory as [32 tokens][64 outputs], so that a token's 64 outputs
-                    // leave as one contiguous run.
+                    // even lanes hold gate, their odd neighbours up: the even lane of a pair takes the even
+                    // tokens, the odd lane the odd ones.  The result is rounded to bfloat16: the fast
+                    // exponential and division are exact enough.
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float mine = __uint_as_float(v[j]);
                         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                        // the result is rounded to bfloat16: the fast exponential and division are exact enough
-                        if (!(lane & 1))
-                            stg[j * 65 + ((warp * 32 + lane) >> 1)] = __fdividef(mine, 1.0f + __expf(-mine)) * other;
+                        if ((j & 1) == (lane & 1)) {
+                            const float g = (lane & 1) ? other : mine, uu = (lane & 1) ? mine : other;
+                            st[j * 17 + (lane >> 1)] = __fdividef(g, 1.0f + __expf(-g)) * uu;
+                        }
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    for (int idx = tid; idx < 32 * 64; idx += 128) {
-                        const int j = idx >> 6, c = idx & 63;
-                        if (tok0 + j < row_end && n0 + 2 * c + 1 < p.N)
-                            static_cast<TOut*>(p.out)[(long long)(tok0 + j) * p.ldo + (n0 >> 1) + c] =
-                                from_f32<TOut>(stg[j * 65 + c]);
+                    __syncwarp();
+                    TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + (colw >> 1);
+                    if (vec_ok && sizeof(TOut) == 2) {
+                        // 32 tokens x 16 outputs: a lane stores 8 outputs (16 bytes) of one token, two passes
+#pragma unroll
+                        for (int pass = 0; pass < 2; ++pass) {
+                            const int j = pass * 16 + (lane >> 1), seg = (lane & 1) * 8;
+                            if (j < n_valid && colw + 2 * seg + 15 < p.N) {
+                                const float* r = st + j * 17 + seg;
+                                uint4 pk;
+                                pk.x = pack2(r[0], r[1]); pk.y = pack2(r[2], r[3]);
+                                pk.z = pack2(r[4], r[5]); pk.w = pack2(r[6], r[7]);
+                                *reinterpret_cast<uint4*>(o + (long long)j * p.ldo + seg) = pk;
+                            }
+                        }
+                    } else {
+                        for (int idx = lane; idx < 32 * 16; idx += 32) {
+                            const int j = idx >> 4, c = idx & 15;
+                            if (j < n_valid && colw + 2 * c + 1 < p.N) o[(long long)j * p.ldo + c] = from_f32<TOut>(st[j * 17 + c]);
+                        }
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                } else if (EPI == EPI_ADD) {
-                    float* o = static_cast<float*>(p.out) + (long long)tok0 * p.ldo + col;
-                    float old[32];                              // all of the chunk's residual loads in flight
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        old[i] = (col_ok && tok0 + i < row_end) ? o[(long long)i * p.ldo] : 0.f;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col_ok && tok0 + i < row_end) o[(long long)i * p.ldo] = old[i] + __uint_as_float(v[i]);
+                    __syncwarp();
                 } else {
-                    TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + col;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col_ok && tok0 + j < row_end)
-                            o[(long long)j * p.ldo] = from_f32<TOut>(__uint_as_float(v[j]) + bias);
+                    for (int j = 0; j < 32; ++j) st[j * 33 + lane] = __uint_as_float(v[j]) + bias;
+                    __syncwarp();
+                    if (EPI == EPI_ADD) {
+                        float* o = static_cast<float*>(p.out) + (long long)tok0 * p.ldo + colw;
+                        if (vec_ok) {
+                            // 32 tokens x 32 columns: a lane owns 4 columns (16 bytes) of one token, eight passes;
+                            // all eight loads of the residual are in flight before the first store
+                            const int seg = (lane & 7) * 4;
+                            const bool cok = colw + seg + 3 < p.N;
+                            float4 old[8];
+#pragma unroll
+                            for (int pass = 0; pass < 8; ++pass) {
+                                const int j = pass * 4 + (lane >> 3);
+                                old[pass] = (cok && j < n_valid)
+                                                ? *reinterpret_cast<const float4*>(o + (long long)j * p.ldo + seg)
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+#pragma unroll
+                            for (int pass = 0; pass < 8; ++pass) {
+                                const int j = pass * 4 + (lane >> 3);
+                                if (cok && j < n_valid) {
+                                    const float* r = st + j * 33 + seg;
+                                    float4 nv = old[pass];
+                                    nv.x += r[0]; nv.y += r[1]; nv.z += r[2]; nv.w += r[3];
+                                    *reinterpret_cast<float4*>(o + (long long)j * p.ldo + seg) = nv;
+                                }
+                            }
+                        } else {
+                            for (int j = 0; j < n_valid; ++j)
+                                if (col_ok) o[(long long)j * p.ldo + lane] += st[j * 33 + lane];
+                        }
+                    } else {
+                        TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + colw;
+                        if (vec_ok && sizeof(TOut) == 4) {
+                            const int seg = (lane & 7) * 4;
+                            const bool cok = colw + seg + 3 < p.N;
+#pragma unroll
+                            for (int pass = 0; pass < 8; ++pass) {
+                                const int j = pass * 4 + (lane >> 3);
+                                if (cok && j < n_valid) {
+                                    const float* r = st + j * 33 + seg;
+                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + (long long)j * p.ldo + seg) =
+                                        make_float4(r[0], r[1], r[2], r[3]);
+                                }
+                            }
+                        } else if (vec_ok && sizeof(TOut) == 2) {
+                            const int seg = (lane & 3) * 8;
+                            const bool cok = colw + seg + 7 < p.N;
+#pragma unroll
+                            for (int pass = 0; pass < 4; ++pass) {
+                                const int j = pass * 8 + (lane >> 2);
+                                if (cok && j < n_valid) {
+                                    const float* r = st + j * 33 + seg;
+                                    uint4 pk;
+                                    pk.x = pack2(r[0], r[1]); pk.y = pack2(r[2], r[3]);
+                                    pk.z = pack2(r[4], r[5]); pk.w = pack2(r[6], r[7]);
+                                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + (long long)j * p.ldo + seg) = pk;
+                                }
+                            }
+                        } else {
+                            for (int j = 0; j < n_valid; ++j)
+                                if (col_ok) o[(long long)j * p.ldo + lane] = from_f32<TOut>(st[j * 33 + lane]);
+                        }
+                    }
+                    __syncwarp();
                 }
             }
             // this accumulator may be written again
@@ -328,7 +407,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
         __syncthreads();
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * TT))
                      : "memory");
     }
@@ -381,7 +460,7 @@ template <int EPI, typename TOut>
 void launch(const CUtensorMap& mw, const CUtensorMap& m64, const CUtensorMap& m128, const CUtensorMap& m256,
             const TcParams& p, int nx, int total_tiles, cudaStream_t stream) {
     constexpr int STAGES = 4;
-    const size_t smem = (size_t)STAGES * (BM * BK * 2 + TT * BK * 2) + 32 * 65 * sizeof(float) + 1024;
+    const size_t smem = (size_t)STAGES * (BM * BK * 2 + TT * BK * 2) + EPI_WARPS * 32 * 33 * sizeof(float) + 1024;
     auto kern = gemm_tc_kernel<STAGES, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
