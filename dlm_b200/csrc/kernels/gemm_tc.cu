@@ -160,11 +160,14 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty) {
 
 // Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulators in tensor memory
 // alternate, so that the epilogue of one tile runs while the MMAs of the next are issued.
+// Token tiles are fetched with the smallest of eight boxes (32, 64, ..., 256 rows) that holds the tile's tokens,
+// so that a short group does not cost the bandwidth of a full one.
+struct TokenMaps { CUtensorMap m[8]; };
+
 template <int STAGES, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a64,
-               const __grid_constant__ CUtensorMap map_a128, const __grid_constant__ CUtensorMap map_a256,
-               TcParams p, int nx, int total_tiles) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_a, TcParams p, int nx,
+               int total_tiles) {
     constexpr uint32_t W_BYTES = BM * BK * 2, A_MAX_BYTES = TT * BK * 2, STAGE_BYTES = W_BYTES + A_MAX_BYTES;
     // M = 128, bfloat16 x bfloat16 -> float32, both operands K-major; N is filled in per tile
     constexpr uint32_t IDESC0 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BM >> 4) << 24);
@@ -208,8 +211,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (ti.expert < 0) continue;
                 const int n0 = (tile % nx) * BM;
                 const int n_tok = ti.row_end - ti.row_begin;
-                const int box = n_tok <= 64 ? 64 : (n_tok <= 128 ? 128 : 256);
-                const CUtensorMap* map_a = box == 64 ? &map_a64 : (box == 128 ? &map_a128 : &map_a256);
+                const int bi = (n_tok + 31) / 32 - 1;         // box of 32 * (bi + 1) rows
+                const int box = 32 * (bi + 1);
+                const CUtensorMap* map_a = &maps_a.m[bi];
                 const uint32_t tx = W_BYTES + (uint32_t)box * BK * 2;
                 const int w_row = (p.expert_offsets != nullptr ? ti.expert * p.N : 0) + n0;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
@@ -457,14 +461,14 @@ int sm_count() {
 }
 
 template <int EPI, typename TOut>
-void launch(const CUtensorMap& mw, const CUtensorMap& m64, const CUtensorMap& m128, const CUtensorMap& m256,
-            const TcParams& p, int nx, int total_tiles, cudaStream_t stream) {
+void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int nx, int total_tiles,
+            cudaStream_t stream) {
     constexpr int STAGES = 4;
     const size_t smem = (size_t)STAGES * (BM * BK * 2 + TT * BK * 2) + EPI_WARPS * 32 * 33 * sizeof(float) + 1024;
     auto kern = gemm_tc_kernel<STAGES, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
-    kern<<<grid, THREADS, smem, stream>>>(mw, m64, m128, m256, p, nx, total_tiles);
+    kern<<<grid, THREADS, smem, stream>>>(mw, ma, p, nx, total_tiles);
 }
 
 }  // namespace
@@ -493,11 +497,12 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
     DLM_CHECK(bias == nullptr || epilogue == EPI_STORE, "gemm: a bias goes with the store epilogue only");
-    CUtensorMap mw, m64, m128, m256;
+    CUtensorMap mw;
+    TokenMaps ma;
     const long long w_rows = expert_offsets ? (long long)num_experts * N : N;
-    if (!make_map(&mw, w, w_rows, K, ldw, BM) || !make_map(&m64, a, M, K, lda, 64) ||
-        !make_map(&m128, a, M, K, lda, 128) || !make_map(&m256, a, M, K, lda, 256))
-        return false;
+    if (!make_map(&mw, w, w_rows, K, ldw, BM)) return false;
+    for (int i = 0; i < 8; ++i)
+        if (!make_map(&ma.m[i], a, M, K, lda, 32 * (i + 1))) return false;
     TcParams p{expert_offsets, num_experts, bias, out, ldo, M, N, K, error_flag_ptr()};
     int t_tiles = (M + TT - 1) / TT;
     if (expert_offsets != nullptr) t_tiles += num_experts;
@@ -506,11 +511,11 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     const int total_tiles = nx * t_tiles;
     const bool f32 = out_dtype == F32;
     switch (epilogue) {
-        case EPI_STORE: if (f32) launch<EPI_STORE, float>(mw, m64, m128, m256, p, nx, total_tiles, stream);
-                        else launch<EPI_STORE, __nv_bfloat16>(mw, m64, m128, m256, p, nx, total_tiles, stream); break;
-        case EPI_ADD: launch<EPI_ADD, float>(mw, m64, m128, m256, p, nx, total_tiles, stream); break;
-        default: if (f32) launch<EPI_SWIGLU, float>(mw, m64, m128, m256, p, nx, total_tiles, stream);
-                 else launch<EPI_SWIGLU, __nv_bfloat16>(mw, m64, m128, m256, p, nx, total_tiles, stream); break;
+        case EPI_STORE: if (f32) launch<EPI_STORE, float>(mw, ma, p, nx, total_tiles, stream);
+                        else launch<EPI_STORE, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;
+        case EPI_ADD: launch<EPI_ADD, float>(mw, ma, p, nx, total_tiles, stream); break;
+        default: if (f32) launch<EPI_SWIGLU, float>(mw, ma, p, nx, total_tiles, stream);
+                 else launch<EPI_SWIGLU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;
     }
     check_launch("gemm_tc");
     return true;
