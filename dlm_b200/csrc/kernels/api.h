@@ -89,4 +89,9 @@ void sample(const float* logits, int32_t* out, int N, int V, const float* params
 // an expert id outside the table).  Returns the flag and clears it.
 int take_error_flag();
 
+// Whether the small kernels are launched so that each may start while the one before it ends
+// (programmatic dependent launch; on unless DLM_B200_NO_PDL=1).
+bool dep_launch_enabled();
+void set_dep_launch(bool on);
+
 }  // namespace dlmk

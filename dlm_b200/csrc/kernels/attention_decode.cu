@@ -226,9 +226,11 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 }
 
 template <typename T>
-__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              const int32_t* __restrict__ cu_q, T* __restrict__ out, int nh, int hd,
+__global__ void attention_decode_merge_kernel(const float* part_o, const float* part_ml,
+                                              const int32_t* __restrict__ cu_q, T* out, int nh, int hd,
                                               int n_splits) {
+    dep_wait();
+    dep_launch_next();
     const int r = blockIdx.x, h = blockIdx.y;
     if (cu_q[r + 1] - cu_q[r] != 1) return;
     const long long base = ((long long)r * nh + h) * n_splits;
@@ -343,9 +345,9 @@ void attention_decode(const void* q, const void* k_cache, const void* v_cache, c
     check_launch("attention_decode");
     dim3 mgrid(R, nh);
     if (dtype == F32)
-        attention_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<float>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
     else
-        attention_decode_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
     check_launch("attention_decode_merge");
 }
 
@@ -359,9 +361,9 @@ void attention_decode_merge(const float* part_o, const float* part_ml, const int
     if (R <= 0) return;
     dim3 mgrid(R, nh);
     if (dtype == F32)
-        attention_decode_merge_kernel<float><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<float>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<float*>(out), nh, hd, n_splits);
     else
-        attention_decode_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
+        launch_dep(attention_decode_merge_kernel<__nv_bfloat16>, mgrid, 128, 0, stream, part_o, part_ml, cu_q, static_cast<__nv_bfloat16*>(out), nh, hd, n_splits);
     check_launch("attention_decode_merge");
 }
 

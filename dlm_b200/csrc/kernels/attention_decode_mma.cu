@@ -46,14 +46,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
-attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                            const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
+attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache,
+                            const __nv_bfloat16* v_cache, const int32_t* __restrict__ block_table,
                             int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
-                            float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int page_size,
+                            float* part_o, float* part_ml, int nh, int nkv, int page_size,
                             int page_shift, int total_pages, int window, float scale_log2, int chunk, int n_splits,
                             int head_passes, int* err) {
     constexpr int PITCH = HD + 8;
     constexpr int KS = HD / 16, DT = HD / 8, CPR = HD / 8;
+    dep_wait();
+    dep_launch_next();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [ROWS][PITCH]
     __nv_bfloat16* Ks = Qs + ROWS * PITCH;                               // [2][BKV][PITCH]
@@ -250,7 +252,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
     if ((page_size & (page_size - 1)) == 0) { shift = 0; while ((1 << shift) < page_size) ++shift; }
     auto kern = attention_decode_mma_kernel<HD>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<grid, WARPS * 32, smem, stream>>>(
+    launch_dep(kern, grid, WARPS * 32, smem, stream,
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv,
         page_size, shift, total_pages, window, scale * 1.4426950408889634f, chunk, n_splits, head_passes,

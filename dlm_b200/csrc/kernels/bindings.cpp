@@ -82,4 +82,6 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                           st(stream));
     });
     m.def("take_error_flag", &dlmk::take_error_flag);
+    m.def("dep_launch_enabled", &dlmk::dep_launch_enabled);
+    m.def("set_dep_launch", &dlmk::set_dep_launch);
 }

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 namespace dlmk {
 
@@ -52,6 +53,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     float t = 0.f;
     for (int i = 0; i < nwarp; ++i) t += scratch[i];
     return t;
+}
+
+// Programmatic dependent launch.  A kernel launched through launch_dep() may be made resident
+// while the kernel before it in the stream is still running, as soon as every block of that kernel
+// has called dep_launch_next() or ended.  It must call dep_wait() before it reads anything an earlier
+// kernel wrote and before it writes anything at all; dep_wait() returns when the earlier kernel
+// has ended and its writes are visible.  Every block calls dep_wait() before it ends, so that
+// "this kernel has ended" implies "all earlier kernels have ended".  What a kernel does before
+// dep_wait() (index arithmetic, loads of weights, which no kernel writes) overlaps the end of the
+// kernel before it.  Launched in the ordinary way both calls do nothing.  Pointers to what earlier
+// kernels write (and to what this kernel writes) are not declared __restrict__ in such kernels:
+// the compiler may move an access through a __restrict__ pointer across dep_wait(), which is an
+// assembly statement that clobbers memory and so orders every other access.
+__device__ __forceinline__ void dep_launch_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Whether launch_dep() asks for the early launch (off: DLM_B200_NO_PDL=1, or set_dep_launch(false)).
+bool dep_launch_enabled();
+void set_dep_launch(bool on);
+
+template <typename... P, typename... A>
+inline void launch_dep(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dep_launch_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);   // an error shows in check_launch()
 }
 
 // Device pointer of the host-mapped error flag (see take_error_flag in api.h).

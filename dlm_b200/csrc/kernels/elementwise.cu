@@ -1,6 +1,8 @@
 // Memory-bound kernels: embedding gather, RMSNorm, rotary + paged key/value write,
 // combination of expert outputs into the residual.
 #include "api.h"
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace dlmk {
@@ -22,6 +24,19 @@ int* error_flag_ptr() {
     return g_flag_dev;
 }
 
+namespace {
+int g_dep_launch = -1;
+}
+
+bool dep_launch_enabled() {
+    if (g_dep_launch < 0) {
+        const char* off = std::getenv("DLM_B200_NO_PDL");
+        g_dep_launch = (off != nullptr && off[0] != '\0' && off[0] != '0') ? 0 : 1;
+    }
+    return g_dep_launch == 1;
+}
+void set_dep_launch(bool on) { g_dep_launch = on ? 1 : 0; }
+
 int take_error_flag() {
     if (g_flag_host == nullptr) return 0;
     int v = *reinterpret_cast<volatile int*>(g_flag_host);
@@ -33,8 +48,10 @@ int take_error_flag() {
 namespace {
 
 template <typename T>
-__global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out,
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ table, float* out,
                              int H, int V, int* err) {
+    dep_wait();
+    dep_launch_next();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (long long)t * H;
@@ -49,9 +66,11 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __rest
 
 // ---------------------------------------------------------------------- rmsnorm
 template <typename TOut>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOut* __restrict__ out,
-                               const int32_t* __restrict__ rows, int H, float eps) {
+__global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut* out,
+                               const int32_t* rows, int H, float eps) {
     __shared__ float scratch[32];
+    dep_wait();
+    dep_launch_next();
     const int r = blockIdx.x;
     const float* xr = x + (long long)(rows ? rows[r] : r) * H;
     float ss = 0.f;
@@ -70,12 +89,14 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // pair index only, so each block computes the rotary_dim / 2 sines and cosines once (in shared memory); then
 // threads run over (head, pair) of the q and k heads, over the unrotated dims, and over the v elements.
 template <typename T>
-__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ positions,
+__global__ void rope_kv_write_kernel(const float* qkv, const int32_t* __restrict__ positions,
                                      const float* __restrict__ inv_freq, int rotary_dim,
-                                     const int32_t* __restrict__ slots, T* __restrict__ q_out, T* __restrict__ k_cache,
-                                     T* __restrict__ v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
+                                     const int32_t* __restrict__ slots, T* q_out, T* k_cache,
+                                     T* v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
                                      int* err) {
     extern __shared__ float sc[];                  // [2][rotary_dim / 2]: sines, cosines
+    dep_wait();
+    dep_launch_next();
     const int t = blockIdx.x;
     const int Q = nh * hd, KV = nkv * hd;
     const float* row = qkv + (long long)t * (Q + 2 * KV);
@@ -139,8 +160,10 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int32_
 }
 
 // ------------------------------------------------------------------ row gather
-__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ rows,
-                                   uint4* __restrict__ out, int chunks) {
+__global__ void gather_rows_kernel(const uint4* src, const int32_t* rows,
+                                   uint4* out, int chunks) {
+    dep_wait();
+    dep_launch_next();
     const int r = blockIdx.x;
     const uint4* s = src + (long long)rows[r] * chunks;
     uint4* o = out + (long long)r * chunks;
@@ -148,9 +171,11 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t*
 }
 
 // ------------------------------------------------------------------ moe combine
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ dest,
-                                   const float* __restrict__ wts, const float* __restrict__ shared,
-                                   const float* __restrict__ gate, float* __restrict__ resid, int H, int k) {
+__global__ void moe_combine_kernel(const float* y, const int32_t* dest,
+                                   const float* wts, const float* shared,
+                                   const float* gate, float* resid, int H, int k) {
+    dep_wait();
+    dep_launch_next();
     const int t = blockIdx.x;
     float* r = resid + (long long)t * H;
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += blockDim.x * gridDim.y) {
@@ -173,8 +198,8 @@ void embed(const int32_t* tokens, const void* table, float* out, int T, int H, i
     if (T <= 0) return;
     int* err = error_flag_ptr();
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == F32) embed_kernel<float><<<T, threads, 0, stream>>>(tokens, static_cast<const float*>(table), out, H, V, err);
-    else embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, static_cast<const __nv_bfloat16*>(table), out, H, V, err);
+    if (dtype == F32) launch_dep(embed_kernel<float>, T, threads, 0, stream, tokens, static_cast<const float*>(table), out, H, V, err);
+    else launch_dep(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, static_cast<const __nv_bfloat16*>(table), out, H, V, err);
     check_launch("embed");
 }
 
@@ -182,8 +207,8 @@ void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int
              int out_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    if (out_dtype == F32) rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, static_cast<float*>(out), rows, H, eps);
-    else rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, static_cast<__nv_bfloat16*>(out), rows, H, eps);
+    if (out_dtype == F32) launch_dep(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, static_cast<float*>(out), rows, H, eps);
+    else launch_dep(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, static_cast<__nv_bfloat16*>(out), rows, H, eps);
     check_launch("rmsnorm");
 }
 
@@ -201,11 +226,11 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
     dim3 grid(T, slices);
     const size_t smem = inv_freq != nullptr ? sizeof(float) * rotary_dim : 0;
     if (dtype == F32)
-        rope_kv_write_kernel<float><<<grid, threads, smem, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+        launch_dep(rope_kv_write_kernel<float>, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), nh, nkv, hd,
             page_size, total_pages, err);
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, smem, stream>>>(qkv, positions, inv_freq, rotary_dim, slots,
+        launch_dep(rope_kv_write_kernel<__nv_bfloat16>, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
     check_launch("rope_kv_write");
@@ -216,8 +241,8 @@ void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, in
     if (n_rows <= 0) return;
     const int bytes = width * (dtype == F32 ? 4 : 2);
     DLM_CHECK(bytes % 16 == 0, "gather_rows: a row must be a multiple of 16 bytes");
-    gather_rows_kernel<<<n_rows, 128, 0, stream>>>(static_cast<const uint4*>(src), rows, static_cast<uint4*>(out),
-                                                   bytes / 16);
+    launch_dep(gather_rows_kernel, n_rows, 128, 0, stream, static_cast<const uint4*>(src), rows,
+               static_cast<uint4*>(out), bytes / 16);
     check_launch("gather_rows");
 }
 
@@ -226,7 +251,7 @@ void moe_combine(const float* y, const int32_t* dest, const float* wts, const fl
     if (T <= 0) return;
     int slices = (H + 255) / 256;
     if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
-    moe_combine_kernel<<<dim3(T, slices), 256, 0, stream>>>(y, dest, wts, shared, gate, resid, H, k);
+    launch_dep(moe_combine_kernel, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k);
     check_launch("moe_combine");
 }
 

@@ -12,6 +12,9 @@
 // A block of 8 warps covers R weight tiles x S slices of K (R * S = 8); the S partial sums of
 // a tile are added in a fixed order through shared memory, so a result does not depend on
 // what else was in the batch.
+//
+// The kernel may start while the kernel before it ends (see dep_wait in common.cuh): a dense
+// product asks its weights into the L2 cache before it waits for its activations.
 #include <mma.h>
 
 #include "api.h"
@@ -44,6 +47,10 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
@@ -63,10 +70,30 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) 
     const int r = warp / S, s = warp % S;
     const int tile = blockIdx.x * R + r;
     const int n_base = tile * 16;
+    const bool tile_ok = n_base < p.N;
+    const int k_begin = s * p.k_chunk;
+    const int k_end = min(p.K, k_begin + p.k_chunk);
+    // weight rows of this lane (clamped to a valid row; rows beyond N are never stored)
+    const int wr0 = min(n_base + g, p.N - 1), wr1 = min(n_base + g + 8, p.N - 1);
 
     int row0 = 0, m_count = p.M;
     const __nv_bfloat16* w = p.w;
-    if (p.expert_offsets != nullptr) {
+    if (p.expert_offsets == nullptr) {
+        // no kernel writes weights: this warp's share of them is asked into the L2 cache while the
+        // kernel before this one ends (one request per 128 bytes, all inside the matrix)
+        if (tile_ok) {
+            const __nv_bfloat16* r0 = w + (long long)wr0 * p.ldw;
+            const __nv_bfloat16* r1 = w + (long long)wr1 * p.ldw;
+            for (int k = k_begin + 64 * t; k < k_end; k += 256) {
+                prefetch_l2(r0 + k);
+                prefetch_l2(r1 + k);
+            }
+        }
+        dep_wait();
+        dep_launch_next();
+    } else {
+        dep_wait();
+        dep_launch_next();
         const int e = blockIdx.y;
         row0 = p.expert_offsets[e];
         m_count = p.expert_offsets[e + 1] - row0;
@@ -74,12 +101,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) 
         if (row0 + m_count > p.M) m_count = p.M - row0;
         w += (long long)e * p.w_expert_stride;
     }
-
-    const bool tile_ok = n_base < p.N;
-    const int k_begin = s * p.k_chunk;
-    const int k_end = min(p.K, k_begin + p.k_chunk);
-    // weight rows of this lane (clamped to a valid row; rows beyond N are never stored)
-    const int wr0 = min(n_base + g, p.N - 1), wr1 = min(n_base + g + 8, p.N - 1);
     const __nv_bfloat16* w0 = w + (long long)wr0 * p.ldw + 8 * t;
     const __nv_bfloat16* w1 = w + (long long)wr1 * p.ldw + 8 * t;
 
@@ -174,9 +195,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) 
 template <int NT, typename TOut>
 void launch_nt(const SmallParams& p, int epilogue, dim3 grid, cudaStream_t stream) {
     switch (epilogue) {
-        case EPI_STORE: gemm_smallm_kernel<NT, EPI_STORE, TOut><<<grid, WARPS * 32, 0, stream>>>(p); break;
-        case EPI_ADD: gemm_smallm_kernel<NT, EPI_ADD, float><<<grid, WARPS * 32, 0, stream>>>(p); break;
-        default: gemm_smallm_kernel<NT, EPI_SWIGLU, TOut><<<grid, WARPS * 32, 0, stream>>>(p); break;
+        case EPI_STORE: launch_dep(gemm_smallm_kernel<NT, EPI_STORE, TOut>, grid, WARPS * 32, 0, stream, p); break;
+        case EPI_ADD: launch_dep(gemm_smallm_kernel<NT, EPI_ADD, float>, grid, WARPS * 32, 0, stream, p); break;
+        default: launch_dep(gemm_smallm_kernel<NT, EPI_SWIGLU, TOut>, grid, WARPS * 32, 0, stream, p); break;
     }
 }
 

@@ -33,10 +33,12 @@ constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
 
 template <typename TX, typename T, bool VEC>
 __global__ void __launch_bounds__(ROUTER_THREADS)
-router_logits_kernel(const TX* __restrict__ h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
-                     float* __restrict__ logits, int H, int rows) {
+router_logits_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
+                     float* logits, int H, int rows) {
     extern __shared__ float smem[];
     __shared__ float scratch[32];
+    dep_wait();
+    dep_launch_next();
     float* x = smem;            // [H]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float ss = 0.f;
@@ -81,10 +83,12 @@ constexpr int ROUTER_EW = 4;     // experts per warp in the many-token kernel
 
 template <typename TX, typename T>
 __global__ void __launch_bounds__(ROUTER_THREADS)
-router_logits_multi_kernel(const TX* __restrict__ h, const T* __restrict__ w, const float* __restrict__ norm_w,
-                           float eps, float* __restrict__ logits, int T_, int H, int rows) {
+router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w,
+                           float eps, float* logits, int T_, int H, int rows) {
     extern __shared__ float smem[];               // [ROUTER_TB][H]
     __shared__ float scratch[32];
+    dep_wait();
+    dep_launch_next();
     const int t0 = blockIdx.x * ROUTER_TB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = min(ROUTER_TB, T_ - t0);
     for (int j = 0; j < ROUTER_TB; ++j) {
@@ -145,9 +149,11 @@ router_logits_multi_kernel(const TX* __restrict__ h, const T* __restrict__ w, co
 // Softmax over the experts, top-k (ties: lower index), optional renormalisation, the shared expert's
 // sigmoid gate.  One warp per token.
 __global__ void __launch_bounds__(128)
-router_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids, float* __restrict__ wts,
-                     float* __restrict__ gate, int T, int E, int k, int norm, int has_gate) {
+router_select_kernel(const float* logits, int32_t* ids, float* wts,
+                     float* gate, int T, int E, int k, int norm, int has_gate) {
     extern __shared__ float smem[];
+    dep_wait();
+    dep_launch_next();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= T) return;
@@ -199,9 +205,11 @@ router_select_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids
 constexpr int PERMUTE_THREADS = 1024;
 
 __global__ void __launch_bounds__(PERMUTE_THREADS)
-moe_permute_kernel(const int32_t* __restrict__ ids, int n, int k, int E, int32_t* __restrict__ offsets,
-                   int32_t* __restrict__ rows, int32_t* __restrict__ dest, int* err) {
+moe_permute_kernel(const int32_t* ids, int n, int k, int E, int32_t* offsets,
+                   int32_t* rows, int32_t* dest, int* err) {
     extern __shared__ int sm[];
+    dep_wait();
+    dep_launch_next();
     int* count = sm;          // [E]
     int* cursor = sm + E;     // [E]
     const int tid = threadIdx.x;
@@ -254,8 +262,8 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     {                                                                                                         \
         auto kern = router_logits_multi_kernel<TX, TW>;                                                       \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_multi);             \
-        kern<<<mgrid, ROUTER_THREADS, smem_multi, stream>>>(static_cast<const TX*>(h), static_cast<const TW*>(w), \
-                                                            norm_w, eps, logits, T, H, rows);                 \
+        launch_dep(kern, mgrid, ROUTER_THREADS, smem_multi, stream, static_cast<const TX*>(h),                \
+                   static_cast<const TW*>(w), norm_w, eps, logits, T, H, rows);                               \
     }
         if (dtype == F32) DLM_ROUTER_MULTI(float, float)
         else if (norm_w != nullptr) DLM_ROUTER_MULTI(float, __nv_bfloat16)
@@ -268,8 +276,8 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     {                                                                                                         \
         auto kern = router_logits_kernel<TX, TW, VEC>;                                                        \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
-        kern<<<grid, ROUTER_THREADS, smem, stream>>>(static_cast<const TX*>(h), static_cast<const TW*>(w),    \
-                                                     norm_w, eps, logits, H, rows);                           \
+        launch_dep(kern, grid, ROUTER_THREADS, smem, stream, static_cast<const TX*>(h),                       \
+                   static_cast<const TW*>(w), norm_w, eps, logits, H, rows);                                  \
     }
     // with norm_w the activations are the 32-bit residual whatever the weights' dtype
     if (dtype == F32) { if (vec) DLM_ROUTER(float, float, true) else DLM_ROUTER(float, float, false) }
@@ -281,8 +289,8 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     const int wpb = 4;
     const size_t smem2 = sizeof(float) * (size_t)wpb * (E + 1);
     cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    router_select_kernel<<<(T + wpb - 1) / wpb, wpb * 32, smem2, stream>>>(logits, ids, wts, gate, T, E, k, norm,
-                                                                           has_gate);
+    launch_dep(router_select_kernel, (T + wpb - 1) / wpb, wpb * 32, smem2, stream, logits, ids, wts, gate, T, E, k,
+               norm, has_gate);
     check_launch("router_select");
 }
 
@@ -290,8 +298,8 @@ void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int3
                  cudaStream_t stream) {
     DLM_CHECK(E >= 1 && E <= 4096, "moe_permute: num_experts must be in 1..4096");
     DLM_CHECK(k >= 1, "moe_permute: k must be >= 1");
-    moe_permute_kernel<<<1, PERMUTE_THREADS, sizeof(int) * 2 * E, stream>>>(ids, n < 0 ? 0 : n, k, E, offsets, rows,
-                                                                            dest, error_flag_ptr());
+    launch_dep(moe_permute_kernel, 1, PERMUTE_THREADS, sizeof(int) * 2 * E, stream, ids, n < 0 ? 0 : n, k, E, offsets,
+               rows, dest, error_flag_ptr());
     check_launch("moe_permute");
 }
 

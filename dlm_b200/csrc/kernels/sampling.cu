@@ -42,10 +42,12 @@ __device__ void block_argmax(float v, int i, float* sv, int* si, float& out_v, i
     out_i = bi;
 }
 
-__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int32_t* __restrict__ out,
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* logits, int32_t* out,
                                                          int V) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    dep_wait();
+    dep_launch_next();
     const float* row = logits + (long long)blockIdx.x * V;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -64,10 +66,12 @@ __global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict
 // warp per row picks among the chunks (lower chunk first on ties, so the first maximum overall).
 constexpr int ARGMAX_CHUNKS = 32;
 
-__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ pv,
-                                                             int32_t* __restrict__ pi, int V) {
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits, float* pv,
+                                                             int32_t* pi, int V) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    dep_wait();
+    dep_launch_next();
     const int row = blockIdx.x, c = blockIdx.y;
     const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
     const int lo = c * per, hi = min(V, lo + per);
@@ -84,8 +88,10 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
     if (threadIdx.x == 0) { pv[row * ARGMAX_CHUNKS + c] = rv; pi[row * ARGMAX_CHUNKS + c] = ri; }
 }
 
-__global__ void argmax_final_kernel(const float* __restrict__ pv, const int32_t* __restrict__ pi,
-                                    int32_t* __restrict__ out) {
+__global__ void argmax_final_kernel(const float* pv, const int32_t* pi,
+                                    int32_t* out) {
+    dep_wait();
+    dep_launch_next();
     const int row = blockIdx.x, lane = threadIdx.x;
     float v = pv[row * ARGMAX_CHUNKS + lane];
     int i = pi[row * ARGMAX_CHUNKS + lane];
@@ -256,10 +262,10 @@ void argmax(const float* logits, int32_t* out, int N, int V, void* scratch, cuda
     if (V >= 16384 && scratch != nullptr) {
         float* pv = static_cast<float*>(scratch);
         int32_t* pi = reinterpret_cast<int32_t*>(pv + (size_t)N * ARGMAX_CHUNKS);
-        argmax_partial_kernel<<<dim3(N, ARGMAX_CHUNKS), 256, 0, stream>>>(logits, pv, pi, V);
-        argmax_final_kernel<<<N, 32, 0, stream>>>(pv, pi, out);
+        launch_dep(argmax_partial_kernel, dim3(N, ARGMAX_CHUNKS), 256, 0, stream, logits, pv, pi, V);
+        launch_dep(argmax_final_kernel, N, 32, 0, stream, pv, pi, out);
     } else {
-        argmax_kernel<<<N, THREADS, 0, stream>>>(logits, out, V);
+        launch_dep(argmax_kernel, N, THREADS, 0, stream, logits, out, V);
     }
     check_launch("argmax");
 }

@@ -8,6 +8,8 @@ the calls capturable in a CUDA graph).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..build import load_kernels
@@ -31,6 +33,36 @@ class KernelError(RuntimeError):
     pass
 
 
+class _Branch:
+    """A piece of a step that may run beside the launching stream.  ``with branch:`` launches
+    what is inside on a second stream that starts after everything launched so far;
+    ``branch.join()`` makes the launching stream wait for it.  Inactive, it does nothing and the
+    work stays in order on the launching stream."""
+
+    def __init__(self, side):
+        self.side = side
+        self.main = None
+        self.ctx = None
+
+    def __enter__(self):
+        if self.side is not None:
+            self.main = torch.cuda.current_stream()
+            self.side.wait_stream(self.main)
+            self.ctx = torch.cuda.stream(self.side)
+            self.ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+            self.ctx = None
+        return False
+
+    def join(self):
+        if self.side is not None and self.main is not None:
+            self.main.wait_stream(self.side)
+
+
 class NativeOps:
     """``fast=False`` keeps every product and the attention on the plain FMA kernels
     (the path the 32-bit mode always takes)."""
@@ -42,10 +74,23 @@ class NativeOps:
         self.fast = 1 if fast else 0
         self.launches = 0        # kernels launched through this object (for the benchmark's count)
         self.tc = bool(self.k.gemm_tc_enabled()) if fast else False
+        self.branches = os.environ.get("DLM_B200_NO_BRANCH", "") in ("", "0")
+        self._side = None        # second stream for branches of a step (made at first use)
 
     @staticmethod
     def _stream() -> int:
         return torch.cuda.current_stream().cuda_stream
+
+    def branch(self, rows: int) -> _Branch:
+        """A branch for work on ``rows`` tokens that is independent of what the caller launches
+        next.  With few rows the kernels stream weights and leave most of the machine idle
+        between them, so two chains side by side fill it better; with many rows each kernel
+        fills the machine alone and the branch stays inactive."""
+        if not self.fast or rows > 64 or not self.branches:
+            return _Branch(None)
+        if self._side is None:
+            self._side = torch.cuda.Stream()
+        return _Branch(self._side)
 
     def check_errors(self) -> None:
         """Raises if a kernel refused an access (page or token id outside its table)."""

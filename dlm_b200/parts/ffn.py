@@ -91,6 +91,13 @@ class SoftmaxTopKMoE(FeedForward):
 
     def forward(self, h, resid, ctx: StepContext, pre_norm=None):
         ops = ctx.rt.ops
+        shared = None
+        branch = ops.branch(h.shape[0])
+        if self.Is:
+            # the shared expert needs nothing from the router: it may run beside the routed experts
+            with branch:
+                sact = ops.linear_swiglu(h, self.ws_gate_up)
+                shared = ops.linear(sact, self.ws_down, None, torch.float32)
         if isinstance(pre_norm, RMSNorm):
             # router logits (and the shared expert's gate) from the 32-bit normalised residual
             ids, wts, gate = ops.router_topk(resid, self.w_router, self.E, self.k, self.norm, self.has_gate,
@@ -100,10 +107,7 @@ class SoftmaxTopKMoE(FeedForward):
         offsets, rows, dest = ops.moe_permute(ids, self.E)
         act = ops.grouped_swiglu(h, self.w_gate_up, offsets, rows)
         y = ops.grouped_linear(act, self.w_down, offsets)
-        shared = None
-        if self.Is:
-            sact = ops.linear_swiglu(h, self.ws_gate_up)
-            shared = ops.linear(sact, self.ws_down, None, torch.float32)
+        branch.join()
         ops.moe_combine(y, dest, wts, shared, gate, resid)
 
 

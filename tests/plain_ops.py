@@ -16,9 +16,23 @@ def _f(t):
     return t.to(torch.float32)
 
 
+class _InOrder:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+    def join(self):
+        pass
+
+
 class PlainOps:
     def check_errors(self):
         pass
+
+    def branch(self, rows):
+        return _InOrder()
 
     # ----------------------------------------------------------------- basic
     def embed(self, tokens, table):
