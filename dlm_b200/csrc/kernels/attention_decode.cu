@@ -286,8 +286,8 @@ void launch_decode(int gt, dim3 grid, size_t smem_bytes, cudaStream_t stream, co
 bool attention_decode_ok(int hd) { return hd % 8 == 0 && hd >= 16 && hd <= 256; }
 
 void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk) {
-    // enough blocks to keep every SM streaming, chunks of at least 64 keys
-    int splits = (592 + R * nkv - 1) / (R * nkv);
+    // one resident wave of blocks (three per multiprocessor), chunks of at least 64 keys
+    int splits = 444 / (R * nkv);
     const int max_splits = (max_kv_len + 63) / 64;
     splits = splits < 1 ? 1 : (splits > max_splits ? max_splits : splits);
     if (splits > 64) splits = 64;

@@ -70,7 +70,10 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
     const int n_heads = min(ROWS, group - pass * ROWS);
     const int len = kv_len[r], p = len - 1;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int j_begin = max(lo, sp * chunk), j_end = min(len, (sp + 1) * chunk);
+    // the request's own visible keys, cut into n_splits equal shares (multiples of 16 keys): every split of a
+    // request has the same work, whatever the longest request of the batch is
+    const int share = (((len - lo) + n_splits - 1) / n_splits + 15) & ~15;
+    const int j_begin = lo + sp * share, j_end = min(len, j_begin + share);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int token = cu_q[r];

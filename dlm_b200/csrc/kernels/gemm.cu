@@ -17,7 +17,14 @@ void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw,
             return;
     }
     if (fast && gemm_smallm_ok(a, lda, w, ldw, w_expert_stride, M, N, K, in_dtype)) {
+        const bool stream_ok = gemm_stream_enabled() &&
+            gemm_stream_ok(a, lda, w, ldw, w_expert_stride, expert_offsets, num_experts, M, N, K, in_dtype);
         if (expert_offsets == nullptr) {
+            if (M <= 64 && stream_ok) {
+                gemm_stream(a, lda, a_rows, w, ldw, w_expert_stride, nullptr, 0, bias, out, ldo, M, N, K, out_dtype,
+                            epilogue, M, stream);
+                return;
+            }
             if (M <= 64) {
                 gemm_smallm(a, lda, a_rows, w, ldw, w_expert_stride, nullptr, 0, bias, out, ldo, M, N, K, out_dtype,
                             epilogue, M, stream);
@@ -29,6 +36,11 @@ void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw,
         } else if (bias == nullptr && (long long)M <= 16LL * num_experts) {
             // few rows per expert on average: stream each active expert's weights once
             const int avg2 = (2 * M + num_experts - 1) / num_experts;     // twice the mean rows per expert
+            if (stream_ok) {
+                gemm_stream(a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, nullptr, out, ldo,
+                            M, N, K, out_dtype, epilogue, avg2 <= 4 ? 8 : (avg2 <= 16 ? 16 : 32), stream);
+                return;
+            }
             gemm_smallm(a, lda, a_rows, w, ldw, w_expert_stride, expert_offsets, num_experts, nullptr, out, ldo, M, N,
                         K, out_dtype, epilogue, avg2 <= 4 ? 8 : (avg2 <= 16 ? 16 : 32), stream);
             return;

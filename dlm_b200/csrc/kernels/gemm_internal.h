@@ -19,6 +19,15 @@ void gemm_smallm(const void* a, int lda, const int32_t* a_rows, const void* w, i
                  const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
                  int K, int out_dtype, int epilogue, int rows_per_pass, cudaStream_t stream);
 
+// The same job with bulk asynchronous copies into shared memory, one persistent block per multiprocessor
+// (bfloat16 inputs only; grouped: at most 1,024 experts can have rows).  Off with DLM_B200_NO_STREAM=1.
+bool gemm_stream_enabled();
+bool gemm_stream_ok(const void* a, int lda, const void* w, int ldw, long long w_expert_stride,
+                    const int32_t* expert_offsets, int num_experts, int M, int N, int K, int in_dtype);
+void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
+                 const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
+                 int K, int out_dtype, int epilogue, int rows_per_pass, cudaStream_t stream);
+
 // Warp-level tensor-core kernel for many rows of A (bfloat16 inputs; same alignment needs as gemm_smallm).
 void gemm_mma(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
               const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,

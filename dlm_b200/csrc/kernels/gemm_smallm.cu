@@ -32,7 +32,7 @@ constexpr int UNROLL = 8;
 struct SmallParams {
     const __nv_bfloat16* a; int lda; const int32_t* a_rows;
     const __nv_bfloat16* w; int ldw; long long w_expert_stride;
-    const int32_t* expert_offsets;
+    const int32_t* expert_offsets; int num_experts;
     const float* bias;
     void* out; int ldo;
     int M, N, K;
@@ -63,6 +63,7 @@ template <int NT, int EPI, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) {
     constexpr int MP = 8 * NT;                       // rows of A per pass
     __shared__ float red[WARPS][16][MP + 1];
+    __shared__ int s_expert;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -94,7 +95,22 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) 
     } else {
         dep_wait();
         dep_launch_next();
-        const int e = blockIdx.y;
+        // blockIdx.y counts the experts that have rows: the first warp finds the expert by a scan of the offsets
+        if (warp == 0) {
+            int found = -1, seen = 0;
+            for (int base = 0; base < p.num_experts && found < 0; base += 32) {
+                const int e = base + lane;
+                const bool has = e < p.num_experts && p.expert_offsets[e + 1] > p.expert_offsets[e];
+                const unsigned mask = __ballot_sync(0xffffffffu, has);
+                const int c = __popc(mask);
+                if ((int)blockIdx.y < seen + c) found = base + (int)__fns(mask, 0, (int)blockIdx.y - seen + 1);
+                seen += c;
+            }
+            if (lane == 0) s_expert = found;
+        }
+        __syncthreads();
+        const int e = s_expert;
+        if (e < 0) return;
         row0 = p.expert_offsets[e];
         m_count = p.expert_offsets[e + 1] - row0;
         if (m_count <= 0) return;
@@ -219,9 +235,10 @@ void gemm_smallm(const void* a, int lda, const int32_t* a_rows, const void* w, i
     SmallParams p;
     p.a = static_cast<const __nv_bfloat16*>(a); p.lda = lda; p.a_rows = a_rows;
     p.w = static_cast<const __nv_bfloat16*>(w); p.ldw = ldw; p.w_expert_stride = w_expert_stride;
-    p.expert_offsets = expert_offsets; p.bias = bias; p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K;
+    p.expert_offsets = expert_offsets; p.num_experts = num_experts; p.bias = bias; p.out = out; p.ldo = ldo; p.M = M; p.N = N; p.K = K;
     const int tiles = (N + 15) / 16;
-    const int groups = expert_offsets ? num_experts : 1;
+    // no more experts have rows than there are rows
+    const int groups = expert_offsets ? (num_experts < M ? num_experts : M) : 1;
     // slices of K: enough blocks to fill the machine, but a slice keeps at least 128 elements
     int S = 8;
     while (S > 1 && ((long long)tiles * groups * S / WARPS > 4096 || K / S < 128)) S >>= 1;

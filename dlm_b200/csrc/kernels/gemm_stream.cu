@@ -1,0 +1,413 @@
+// C = A · W^T for few rows of A (decode steps, and experts that got a handful of tokens), bound by
+// the reading of W: a weight-streaming kernel built on bulk asynchronous copies.
+//
+// One persistent block per multiprocessor walks a contiguous range of work items; an item is a tile
+// of 16 rows of W (of one expert), so that a block reads one long contiguous stretch of memory.
+// A producer warp brings the tile into shared memory, one bulk copy (cp.async.bulk, completion on an
+// mbarrier) per row and up to 4 KB each, three stages deep; rows longer than 2,048 elements come in
+// chunks.  Eight consumer warps split a chunk along K; each multiplies its slice by the rows of A,
+// which it holds in registers, in tensor-core MMAs with the roles swapped (16 rows of W are the MMA's
+// M, 8 rows of A its N; mma.sync m16n8k16, bfloat16 in, 32-bit accumulation), and the eight partial
+// sums of a tile are added in a fixed order through shared memory, one tile late, so that no warp
+// waits for the slowest.  A result does not depend on what else was in the batch.
+//
+// K is walked in blocks of 32.  Lane (g = lane / 4, t = lane % 4) takes the 8 consecutive elements
+// 8t..8t+7 of rows g and g + 8 of the weight tile and of row g of A; the two MMAs of a block take
+// elements {0,1 | 2,3} and {4,5 | 6,7} of those as their k-slices.  A sum does not care in which
+// order its terms are listed, and A and W list them alike.  Rows of a stage are 64 bytes (mod 128)
+// apart, so that the 16-byte reads of a quarter warp fall into distinct banks.
+//
+// Every wait on an mbarrier is bounded: a wait that runs out sets a block-wide flag, all roles
+// leave their loops, the producer waits (bounded again) for its copies in flight, and the kernel
+// reports error 5 through the error flag.
+//
+// The kernel may start while the kernel before it ends (see dep_wait in common.cuh): the producer of
+// a dense product starts to fetch weights, which no kernel writes, before the activations are there.
+#include <cstdlib>
+
+#include "api.h"
+#include "common.cuh"
+#include "gemm_internal.h"
+
+namespace dlmk {
+
+namespace {
+
+constexpr int CW = 8;                        // consumer warps
+constexpr int THREADS = (CW + 1) * 32;       // + the producer warp
+constexpr int RT = 16;                       // rows of W per tile
+constexpr int STAGES = 3;
+constexpr int KC_MAX = 2048;                 // most elements of a row per stage
+constexpr int MAX_ACTIVE = 1024;             // most experts with rows in one launch
+constexpr uint32_t WAIT_LIMIT = 1u << 22;    // try_wait calls before a wait gives up
+
+struct StreamParams {
+    const __nv_bfloat16* a; int lda; const int32_t* a_rows;
+    const __nv_bfloat16* w; int ldw; long long w_expert_stride;
+    const int32_t* expert_offsets; int num_experts;
+    const float* bias;
+    void* out; int ldo;
+    int M, N, K;
+    int tiles;            // ceil(N / RT)
+    int n_chunks, kc;     // chunks of K per tile, elements per chunk (the last may be shorter)
+    int slice;            // elements of a chunk per consumer warp: a multiple of 32, at most 256
+    int pitch;            // bytes between the rows of a stage
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait.  Returns false when it gave up (or another role already had): the caller stops.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// One row piece: global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned.
+__device__ __forceinline__ void bulk_copy(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(const void* p) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
+    return v;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct Work { int expert, row0, m_count, tile; };
+
+// Item `item` of the launch: dense, tile `item` for all rows of A; grouped, tile item % tiles of the
+// (item / tiles)-th expert that has rows.
+__device__ __forceinline__ Work get_work(const StreamParams& p, const int* s_active, int item) {
+    Work wk{0, 0, p.M, item};
+    if (p.expert_offsets != nullptr) {
+        wk.expert = s_active[item / p.tiles];
+        wk.tile = item % p.tiles;
+        wk.row0 = p.expert_offsets[wk.expert];
+        wk.m_count = min(p.expert_offsets[wk.expert + 1], p.M) - wk.row0;
+    }
+    return wk;
+}
+
+template <int NT, int EPI, typename TOut>
+__global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p) {
+    constexpr int MP = 8 * NT;                       // rows of A per pass
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES];     // a stage has arrived
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];    // all consumer warps have read a stage
+    __shared__ __align__(8) uint64_t red_full[2];          // partial sums of a tile written by all consumer warps
+    __shared__ int s_active[MAX_ACTIVE];
+    __shared__ int s_n_active, s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t stage_bytes = (size_t)RT * p.pitch;
+    float* red = reinterpret_cast<float*>(smem + STAGES * stage_bytes);      // [2][CW][16][MP + 1]
+    const bool grouped = p.expert_offsets != nullptr;
+    volatile int* abort_flag = &s_abort;
+
+    if (tid == 0) {
+        s_abort = 0;
+        s_n_active = 1;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CW); }
+        mbar_init(&red_full[0], CW);
+        mbar_init(&red_full[1], CW);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (grouped) {
+        dep_wait();
+        dep_launch_next();
+        __syncthreads();
+        // the experts that have rows, in ascending order
+        if (warp == 0) {
+            int seen = 0;
+            for (int base = 0; base < p.num_experts; base += 32) {
+                const int e = base + lane;
+                const bool has = e < p.num_experts && min(p.expert_offsets[e + 1], p.M) > p.expert_offsets[e];
+                const unsigned mask = __ballot_sync(0xffffffffu, has);
+                const int slot = seen + __popc(mask & ((1u << lane) - 1));
+                if (has && slot < MAX_ACTIVE) s_active[slot] = e;
+                seen += __popc(mask);
+            }
+            if (lane == 0) s_n_active = min(seen, MAX_ACTIVE);
+        }
+    }
+    __syncthreads();
+    const long long total = (long long)s_n_active * p.tiles;
+    const int item_begin = (int)(total * blockIdx.x / gridDim.x);
+    const int item_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+
+    if (warp == CW) {
+        // ------------------------------------------------------------------ producer
+        uint32_t it = 0;                                  // stages issued so far
+        bool ok = true;
+        for (int item = item_begin; item < item_end && ok; ++item) {
+            const Work wk = get_work(p, s_active, item);
+            const int passes = (wk.m_count + MP - 1) / MP;
+            const int row = min(wk.tile * RT + (lane & (RT - 1)), p.N - 1);      // rows beyond N: a valid row again
+            const __nv_bfloat16* src_row = p.w + (long long)wk.expert * p.w_expert_stride + (long long)row * p.ldw;
+            for (int pc = 0; pc < passes * p.n_chunks; ++pc, ++it) {
+                const int c = pc % p.n_chunks;
+                const uint32_t s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const int k0 = c * p.kc;
+                const uint32_t len = (uint32_t)min(p.kc, p.K - k0);
+                if (lane == 0) mbar_expect_tx(&full_bar[s], RT * len * 2);
+                __syncwarp();
+                if (lane < RT) bulk_copy(smem + s * stage_bytes + (size_t)lane * p.pitch, src_row + k0, len * 2, &full_bar[s]);
+            }
+        }
+        if (!grouped) dep_wait();            // every thread waits for the kernel before this one before it ends
+        if (!ok) {
+            // copies in flight must land before the block's shared memory is given up
+            const uint32_t first = it > STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; ++j) {
+                for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+                    if (mbar_try_wait(&full_bar[j % STAGES], (j / STAGES) & 1)) break;
+            }
+        }
+    } else {
+        // ----------------------------------------------------------------- consumers
+        if (!grouped) {
+            dep_wait();
+            dep_launch_next();
+        }
+        const int g = lane >> 2, t = lane & 3;
+        const int kw = warp * p.slice;                   // this warp's first element within a chunk
+        const int nb = p.slice >> 5;                     // its blocks of 32 elements
+        uint32_t it = 0, ep = 0;
+        bool ok = true;
+        uint4 xb[NT][8];
+        long long held = -1;                             // (first row, pass) whose rows of A are in xb (one chunk per tile)
+        struct Done { int out_row0, m_here, n_base; };   // where a finished tile's sums go
+        Done prev{0, 0, 0};
+        // adds the eight partial sums of tile number `e` in a fixed order and stores the results
+        auto finish_tile = [&](uint32_t e, const Done& d) -> bool {
+            if (!mbar_wait(&red_full[e & 1], (e >> 1) & 1, abort_flag)) return false;
+            const float* rb = red + (size_t)(e & 1) * CW * 16 * (MP + 1);
+            if (EPI == EPI_SWIGLU) {
+                // element = (row of A, pair of weight rows)
+                for (int i = tid; i < MP * 8; i += CW * 32) {
+                    const int pr = i & 7, m = i >> 3;
+                    const int n = d.n_base + 2 * pr;
+                    if (m >= d.m_here || n + 1 >= p.N) continue;
+                    float gate = 0.f, up = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < CW; ++ww) {
+                        gate += rb[((size_t)ww * 16 + 2 * pr) * (MP + 1) + m];
+                        up += rb[((size_t)ww * 16 + 2 * pr + 1) * (MP + 1) + m];
+                    }
+                    static_cast<TOut*>(p.out)[(long long)(d.out_row0 + m) * p.ldo + (n >> 1)] =
+                        from_f32<TOut>(silu_f(gate) * up);
+                }
+            } else {
+                for (int i = tid; i < MP * 16; i += CW * 32) {
+                    const int row = i & 15, m = i >> 4;
+                    const int n = d.n_base + row;
+                    if (m >= d.m_here || n >= p.N) continue;
+                    float v = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < CW; ++ww) v += rb[((size_t)ww * 16 + row) * (MP + 1) + m];
+                    const long long o = (long long)(d.out_row0 + m) * p.ldo + n;
+                    if (EPI == EPI_ADD) static_cast<float*>(p.out)[o] += v;
+                    else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(v + (p.bias ? p.bias[n] : 0.f));
+                }
+            }
+            return true;
+        };
+        for (int item = item_begin; item < item_end && ok; ++item) {
+            const Work wk = get_work(p, s_active, item);
+            const int passes = (wk.m_count + MP - 1) / MP;
+            for (int pass = 0; pass < passes && ok; ++pass) {
+                const int m0 = pass * MP;
+                float acc[NT][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+                for (int c = 0; c < p.n_chunks; ++c, ++it) {
+                    const int k0 = c * p.kc;
+                    const int len = min(p.kc, p.K - k0);
+                    // this lane's pieces of the rows of A
+                    const long long key = ((long long)wk.row0 << 20) | (long long)pass;
+                    if (p.n_chunks > 1 || key != held) {
+                        held = key;
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const int m = m0 + nt * 8 + g;
+                            const __nv_bfloat16* arow = nullptr;
+                            if (m < wk.m_count) {
+                                const int src = p.a_rows ? p.a_rows[wk.row0 + m] : wk.row0 + m;
+                                arow = p.a + (long long)src * p.lda + k0 + kw + 8 * t;
+                            }
+#pragma unroll
+                            for (int b = 0; b < 8; ++b) {
+                                xb[nt][b] = make_uint4(0, 0, 0, 0);
+                                if (b < nb && arow != nullptr && kw + 32 * b + 8 * t < len)
+                                    xb[nt][b] = __ldg(reinterpret_cast<const uint4*>(arow + 32 * b));
+                            }
+                        }
+                    }
+                    const uint32_t s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+                    const unsigned char* st = smem + s * stage_bytes + (size_t)(kw + 8 * t) * 2;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        if (b < nb) {
+                            // K is a multiple of 8: a lane's 8 elements are all in or all out
+                            uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
+                            if (kw + 32 * b + 8 * t < len) {
+                                w0 = lds128(st + (size_t)g * p.pitch + 64 * b);
+                                w1 = lds128(st + (size_t)(g + 8) * p.pitch + 64 * b);
+                            }
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                mma_bf16(acc[nt], w0.x, w1.x, w0.y, w1.y, xb[nt][b].x, xb[nt][b].y);
+                                mma_bf16(acc[nt], w0.z, w1.z, w0.w, w1.w, xb[nt][b].z, xb[nt][b].w);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+                }
+                if (!ok) break;
+                // The sums of the tile before this one are finished now, one tile late, so that nobody waits
+                // for the slowest warp: its partial sums have long been written.
+                if (ep > 0 && !finish_tile(ep - 1, prev)) { ok = false; break; }
+                // Partial sums to shared memory: red[ep % 2][warp][weight row][row of A].  The buffer's last
+                // readers (tile ep - 2) were done before they wrote the partial sums of tile ep - 1, which
+                // finish_tile has just waited for.
+                float* mine = red + ((size_t)(ep & 1) * CW + warp) * 16 * (MP + 1);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mine[g * (MP + 1) + nt * 8 + 2 * t] = acc[nt][0];
+                    mine[g * (MP + 1) + nt * 8 + 2 * t + 1] = acc[nt][1];
+                    mine[(g + 8) * (MP + 1) + nt * 8 + 2 * t] = acc[nt][2];
+                    mine[(g + 8) * (MP + 1) + nt * 8 + 2 * t + 1] = acc[nt][3];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_full[ep & 1]);
+                prev = Done{wk.row0 + m0, min(MP, wk.m_count - m0), wk.tile * RT};
+                ++ep;
+            }
+        }
+        if (ok && ep > 0) finish_tile(ep - 1, prev);
+    }
+    __syncthreads();
+    if (tid == 0 && s_abort) *p.err = 5;
+}
+
+int sm_count_stream() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int NT, int EPI, typename TOut>
+void launch_one(const StreamParams& p, int grid, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * RT * p.pitch + 2 * sizeof(float) * CW * 16 * (8 * NT + 1);
+    auto kern = gemm_stream_kernel<NT, EPI, TOut>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_dep(kern, grid, THREADS, smem, stream, p);
+}
+
+template <int NT>
+void launch_nt(const StreamParams& p, int grid, int out_dtype, int epilogue, cudaStream_t stream) {
+    const bool f32 = out_dtype == F32;
+    switch (epilogue) {
+        case EPI_STORE: if (f32) launch_one<NT, EPI_STORE, float>(p, grid, stream);
+                        else launch_one<NT, EPI_STORE, __nv_bfloat16>(p, grid, stream); break;
+        case EPI_ADD: launch_one<NT, EPI_ADD, float>(p, grid, stream); break;
+        default: if (f32) launch_one<NT, EPI_SWIGLU, float>(p, grid, stream);
+                 else launch_one<NT, EPI_SWIGLU, __nv_bfloat16>(p, grid, stream); break;
+    }
+}
+
+}  // namespace
+
+bool gemm_stream_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* off = std::getenv("DLM_B200_NO_STREAM");
+        on = (off != nullptr && off[0] != '\0' && off[0] != '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+bool gemm_stream_ok(const void* a, int lda, const void* w, int ldw, long long w_expert_stride,
+                    const int32_t* expert_offsets, int num_experts, int M, int N, int K, int in_dtype) {
+    if (!(in_dtype == BF16 && M > 0 && N > 0 && K >= 8 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
+          w_expert_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+          (reinterpret_cast<uintptr_t>(w) & 15) == 0))
+        return false;
+    // the list of experts with rows lives in shared memory
+    if (expert_offsets != nullptr && (num_experts < M ? num_experts : M) > MAX_ACTIVE) return false;
+    return true;
+}
+
+void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
+                 const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N,
+                 int K, int out_dtype, int epilogue, int rows_per_pass, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return;
+    DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
+    DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
+    StreamParams p;
+    p.a = static_cast<const __nv_bfloat16*>(a); p.lda = lda; p.a_rows = a_rows;
+    p.w = static_cast<const __nv_bfloat16*>(w); p.ldw = ldw; p.w_expert_stride = w_expert_stride;
+    p.expert_offsets = expert_offsets; p.num_experts = num_experts; p.bias = bias; p.out = out; p.ldo = ldo;
+    p.M = M; p.N = N; p.K = K;
+    p.tiles = (N + RT - 1) / RT;
+    const int nt = rows_per_pass <= 8 ? 1 : (rows_per_pass <= 16 ? 2 : 4);
+    // three stages and the partial sums share 227 KB: the widest pass takes shorter chunks
+    const int kc_max = nt == 4 ? KC_MAX - 256 : KC_MAX;
+    p.n_chunks = (K + kc_max - 1) / kc_max;
+    p.kc = ((K + p.n_chunks - 1) / p.n_chunks + 31) / 32 * 32;
+    if (p.kc > K) p.kc = K;
+    p.slice = ((p.kc + CW - 1) / CW + 31) / 32 * 32;
+    // rows of a stage 64 bytes (mod 128) apart
+    const int row_bytes = p.kc * 2;
+    p.pitch = row_bytes + ((64 - row_bytes % 128) + 128) % 128;
+    p.err = error_flag_ptr();
+    const int groups = expert_offsets ? (num_experts < M ? num_experts : M) : 1;
+    const long long items = (long long)p.tiles * groups;
+    const int grid = (int)(items < sm_count_stream() ? items : sm_count_stream());
+    if (nt == 1) launch_nt<1>(p, grid, out_dtype, epilogue, stream);
+    else if (nt == 2) launch_nt<2>(p, grid, out_dtype, epilogue, stream);
+    else launch_nt<4>(p, grid, out_dtype, epilogue, stream);
+    check_launch("gemm_stream");
+}
+
+}  // namespace dlmk

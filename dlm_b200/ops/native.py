@@ -97,7 +97,8 @@ class NativeOps:
         flag = self.k.take_error_flag()
         if flag:
             what = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
-                    3: "a visible key has no page", 4: "expert id outside the table"}.get(flag, "unknown")
+                    3: "a visible key has no page", 4: "expert id outside the table",
+                    5: "a wait inside a kernel ran out (copy or tensor-core pipeline)"}.get(flag, "unknown")
             raise KernelError(f"a kernel reported error {flag}: {what}")
 
     # ----------------------------------------------------------------- basic
