@@ -94,17 +94,29 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
 
+        // a tile lies within one page when pages are a power of two of at least a tile (tiles are aligned)
+        const bool one_page = page_shift >= 0 && page_size >= BKV;
         auto fill = [&](int stage, int j0) {
             __nv_bfloat16* kd = Ks + (size_t)stage * BKV * PITCH;
             __nv_bfloat16* vd = Vs + (size_t)stage * BKV * PITCH;
+            int tile_page = -1;
+            if (one_page) {
+                const int lp = j0 >> page_shift;
+                tile_page = lp < table_width ? table[lp] : -1;
+            }
             for (int idx = tid; idx < BKV * CPR; idx += WARPS * 32) {
                 const int key = idx / CPR, c = idx % CPR;         // CPR is a compile-time constant
                 const int j = j0 + key;
                 int page = -1, in_page = 0;
                 if (j >= j_begin && j < j_end) {
-                    const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
-                    in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
-                    page = lp < table_width ? table[lp] : -1;
+                    if (one_page) {
+                        page = tile_page;
+                        in_page = j & (page_size - 1);
+                    } else {
+                        const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+                        in_page = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+                        page = lp < table_width ? table[lp] : -1;
+                    }
                     if (page < 0 || page >= total_pages) { *err = 3; page = -1; }
                 }
                 if (page >= 0) {

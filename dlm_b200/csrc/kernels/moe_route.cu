@@ -86,64 +86,80 @@ __global__ void __launch_bounds__(ROUTER_THREADS)
 router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w,
                            float eps, float* logits, int T_, int H, int rows) {
     extern __shared__ float smem[];               // [ROUTER_TB][H]
-    __shared__ float scratch[32];
     dep_wait();
     dep_launch_next();
     const int t0 = blockIdx.x * ROUTER_TB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = min(ROUTER_TB, T_ - t0);
-    for (int j = 0; j < ROUTER_TB; ++j) {
+    // Staging: warp j brings token t0 + j into shared memory and normalises it.  The sum of squares is taken
+    // in the order of router_logits_kernel's block_sum over ROUTER_THREADS threads: lane l keeps one partial sum
+    // for each of that kernel's warps v (its thread 32 v + l takes elements 32 v + l, + ROUTER_THREADS, ...),
+    // every partial sum goes through the same shuffle tree, and the warps' sums are added in order.
+    static_assert(ROUTER_TB == ROUTER_WARPS, "one staging warp per token");
+    {
+        const int j = warp;
         float* x = smem + (size_t)j * H;
         if (j >= nt) {
-            for (int i = tid; i < H; i += blockDim.x) x[i] = 0.f;
-            continue;
-        }
-        float ss = 0.f;
-        for (int i = tid; i < H; i += blockDim.x) {
-            const float v = to_f32(h[(long long)(t0 + j) * H + i]);
-            x[i] = v;
-            ss = fmaf(v, v, ss);
-        }
-        if (norm_w != nullptr) {
-            ss = block_sum(ss, scratch);
-            const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-            for (int i = tid; i < H; i += blockDim.x) x[i] = (x[i] * inv) * norm_w[i];
+            for (int i = lane; i < H; i += 32) x[i] = 0.f;
+        } else {
+            const TX* src = h + (long long)(t0 + j) * H;
+            float part[ROUTER_WARPS];
+#pragma unroll
+            for (int v = 0; v < ROUTER_WARPS; ++v) part[v] = 0.f;
+            for (int base = 0; base < H; base += ROUTER_THREADS) {
+#pragma unroll
+                for (int v = 0; v < ROUTER_WARPS; ++v) {
+                    const int i = base + 32 * v + lane;
+                    if (i < H) {
+                        const float val = to_f32(src[i]);
+                        x[i] = val;
+                        part[v] = fmaf(val, val, part[v]);
+                    }
+                }
+            }
+            if (norm_w != nullptr) {
+                float ss = 0.f;
+#pragma unroll
+                for (int v = 0; v < ROUTER_WARPS; ++v) ss += warp_sum(part[v]);
+                const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+                for (int i = lane; i < H; i += 32) x[i] = (x[i] * inv) * norm_w[i];
+            }
         }
     }
     __syncthreads();
-    // a warp takes ROUTER_EW experts x ROUTER_TB tokens: every activation read from shared memory meets
-    // ROUTER_EW weight rows, every weight meets ROUTER_TB tokens
-    const int e0 = (blockIdx.y * ROUTER_WARPS + warp) * ROUTER_EW;
-    if (e0 >= rows) return;
-    float s[ROUTER_EW][ROUTER_TB];
+    // a warp takes ROUTER_EW experts x ROUTER_TB tokens at a time: every activation read from shared memory
+    // meets ROUTER_EW weight rows, every weight meets ROUTER_TB tokens
+    for (int e0 = warp * ROUTER_EW; e0 < rows; e0 += ROUTER_WARPS * ROUTER_EW) {
+        float s[ROUTER_EW][ROUTER_TB];
 #pragma unroll
-    for (int a = 0; a < ROUTER_EW; ++a)
+        for (int a = 0; a < ROUTER_EW; ++a)
 #pragma unroll
-        for (int j = 0; j < ROUTER_TB; ++j) s[a][j] = 0.f;
-    for (int i = lane * 8; i < H; i += 256) {
-        float wv[ROUTER_EW][8];
+            for (int j = 0; j < ROUTER_TB; ++j) s[a][j] = 0.f;
+        for (int i = lane * 8; i < H; i += 256) {
+            float wv[ROUTER_EW][8];
 #pragma unroll
-        for (int a = 0; a < ROUTER_EW; ++a) {
-            const int e = min(e0 + a, rows - 1);            // rows beyond the table repeat the last one (not stored)
-            load8(w + (long long)e * H + i, wv[a]);
+            for (int a = 0; a < ROUTER_EW; ++a) {
+                const int e = min(e0 + a, rows - 1);            // rows beyond the table repeat the last one (not stored)
+                load8(w + (long long)e * H + i, wv[a]);
+            }
+#pragma unroll
+            for (int j = 0; j < ROUTER_TB; ++j) {
+                const float* x = smem + (size_t)j * H + i;
+                const float4 xa = *reinterpret_cast<const float4*>(x), xb = *reinterpret_cast<const float4*>(x + 4);
+                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                for (int a = 0; a < ROUTER_EW; ++a)
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) s[a][j] = fmaf(xv[q], wv[a][q], s[a][j]);
+            }
         }
 #pragma unroll
-        for (int j = 0; j < ROUTER_TB; ++j) {
-            const float* x = smem + (size_t)j * H + i;
-            const float4 xa = *reinterpret_cast<const float4*>(x), xb = *reinterpret_cast<const float4*>(x + 4);
-            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        for (int a = 0; a < ROUTER_EW; ++a)
 #pragma unroll
-            for (int a = 0; a < ROUTER_EW; ++a)
-#pragma unroll
-                for (int q = 0; q < 8; ++q) s[a][j] = fmaf(xv[q], wv[a][q], s[a][j]);
-        }
+            for (int j = 0; j < ROUTER_TB; ++j) {
+                const float v = warp_sum(s[a][j]);
+                if (lane == 0 && j < nt && e0 + a < rows) logits[(long long)(t0 + j) * rows + e0 + a] = v;
+            }
     }
-#pragma unroll
-    for (int a = 0; a < ROUTER_EW; ++a)
-#pragma unroll
-        for (int j = 0; j < ROUTER_TB; ++j) {
-            const float v = warp_sum(s[a][j]);
-            if (lane == 0 && j < nt && e0 + a < rows) logits[(long long)(t0 + j) * rows + e0 + a] = v;
-        }
 }
 
 // Softmax over the experts, top-k (ties: lower index), optional renormalisation, the shared expert's
@@ -256,8 +272,7 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     const size_t smem_multi = sizeof(float) * (size_t)H * ROUTER_TB;
     if (vec && T >= 32 && smem_multi <= 200 * 1024) {
-        dim3 mgrid((T + ROUTER_TB - 1) / ROUTER_TB,
-                   (rows + ROUTER_WARPS * ROUTER_EW - 1) / (ROUTER_WARPS * ROUTER_EW));
+        dim3 mgrid((T + ROUTER_TB - 1) / ROUTER_TB);
 #define DLM_ROUTER_MULTI(TX, TW)                                                                              \
     {                                                                                                         \
         auto kern = router_logits_multi_kernel<TX, TW>;                                                       \
