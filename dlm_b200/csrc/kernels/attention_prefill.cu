@@ -57,7 +57,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_table,
                          int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int R, int nh, int nkv, int page_size, int total_pages,
-                         int page_shift, int window, float scale_log2, int skip_single, int* err) {
+                         int page_shift, int window, float scale_log2, int skip_single, int n_sm, int* err) {
     constexpr int PITCH = HD + 8;              // elements per shared-memory row (16 bytes of padding)
     constexpr int KS = HD / 16;                // k16 steps over the head dimension
     constexpr int DT = HD / 8;                 // n8 tiles of the output
@@ -69,8 +69,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     __shared__ int s_map[2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int head = blockIdx.x, kvh = head / (nh / nkv);
-    const int bx = (int)gridDim.y - 1 - (int)blockIdx.y;        // late tiles (most keys) first
+    // Work order.  Blocks start in the order of their linear index; with two blocks per multiprocessor the
+    // first n_sm blocks take the heaviest tiles (the latest queries see the most keys), the next n_sm the
+    // lightest in ascending order, so that a multiprocessor's two first blocks add up to about the same work;
+    // the rest follows from heavy to light as blocks end.
+    const int linear = (int)(blockIdx.y * gridDim.x + blockIdx.x), total = (int)(gridDim.x * gridDim.y);
+    int rank = linear;
+    if (linear >= n_sm) rank = linear < 2 * n_sm ? total - 1 - (linear - n_sm) : linear - n_sm;
+    const int head = rank % nh, kvh = head / (nh / nkv);
+    const int bx = (int)gridDim.y - 1 - rank / nh;              // late tiles (most keys) have the low ranks
     if (tid == 0) {
         int acc = 0;
         s_map[0] = -1;
@@ -283,6 +290,16 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
 }
 
+int sm_count_attn() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int HD>
 void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
             const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int R,
@@ -296,7 +313,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
         static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, shift, window,
-        scale * 1.4426950408889634f, skip_single, error_flag_ptr());
+        scale * 1.4426950408889634f, skip_single, sm_count_attn(), error_flag_ptr());
 }
 
 }  // namespace

@@ -65,23 +65,84 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const T* __rest
 }
 
 // ---------------------------------------------------------------------- rmsnorm
-template <typename TOut>
+// Two passes over a row; the second finds it in the L1 cache.
+template <typename TOut> struct Out4;
+template <> struct Out4<float> {
+    static __device__ __forceinline__ void store(float* o, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Out4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* o, float a, float b, float c, float d) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<const uint32_t*>(&lo);
+        v.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(o) = v;
+    }
+};
+
+// The sum of squares of a row has one order, whoever computes it: the row's elements (VEC: its groups of four)
+// are dealt round-robin to 8 x 32 partial sums, partial sum (v, l) takes items 32 v + l, + 256, + 512, ...; each
+// v's 32 partial sums go through a shuffle tree; the eight results are added in order.  WIDE: the eight warps of
+// a block share one row, warp v keeps the partial sums (v, .); else one warp keeps all eight sets for its row and
+// a block holds several rows.  So a row's result does not depend on how many rows the launch has.
+template <typename TOut, bool VEC, bool WIDE>
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut* out,
-                               const int32_t* rows, int H, float eps) {
-    __shared__ float scratch[32];
+                               const int32_t* rows, int n_rows, int H, float eps) {
+    __shared__ float s_part[8];
     dep_wait();
     dep_launch_next();
-    const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = WIDE ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= n_rows) return;
     const float* xr = x + (long long)(rows ? rows[r] : r) * H;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = xr[i];
-        ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TOut* o = out + (long long)r * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TOut>((xr[i] * inv) * w[i]);
+    const int items = VEC ? H / 4 : H;
+    auto square = [&](int i, float acc) -> float {
+        if (VEC) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            acc = fmaf(v.x, v.x, acc); acc = fmaf(v.y, v.y, acc); acc = fmaf(v.z, v.z, acc); acc = fmaf(v.w, v.w, acc);
+        } else {
+            acc = fmaf(xr[i], xr[i], acc);
+        }
+        return acc;
+    };
+    float ss = 0.f;
+    if (WIDE) {
+        float part = 0.f;
+        for (int i = 32 * warp + lane; i < items; i += 256) part = square(i, part);
+        part = warp_sum(part);
+        if (lane == 0) s_part[warp] = part;
+        __syncthreads();
+#pragma unroll
+        for (int v = 0; v < 8; ++v) ss += s_part[v];
+    } else {
+        float part[8];
+#pragma unroll
+        for (int v = 0; v < 8; ++v) part[v] = 0.f;
+        for (int base = 0; base < items; base += 256) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                const int i = base + 32 * v + lane;
+                if (i < items) part[v] = square(i, part[v]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 8; ++v) ss += warp_sum(part[v]);
+    }
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    const int first = WIDE ? threadIdx.x : lane, step = WIDE ? 256 : 32;
+    if (VEC) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        for (int i = first; i < items; i += step) {
+            const float4 v = x4[i], g = __ldg(w4 + i);
+            Out4<TOut>::store(o + 4 * i, (v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
+        }
+    } else {
+        for (int i = first; i < items; i += step) o[i] = from_f32<TOut>((xr[i] * inv) * w[i]);
+    }
 }
 
 // ------------------------------------------------------- rotary + cache write
@@ -159,6 +220,81 @@ __global__ void rope_kv_write_kernel(const float* qkv, const int32_t* __restrict
     }
 }
 
+// The same in steps of four elements (16-byte loads, 8- or 16-byte stores), for head sizes, rotary sizes and
+// addresses that allow it.  Per element the arithmetic is that of rope_kv_write_kernel.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(const float* qkv, const int32_t* __restrict__ positions,
+                                         const float* __restrict__ inv_freq, int rotary_dim,
+                                         const int32_t* __restrict__ slots, T* q_out, T* k_cache,
+                                         T* v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
+                                         int* err) {
+    extern __shared__ float sc[];                  // [2][rotary_dim / 2]: sines, cosines
+    dep_wait();
+    dep_launch_next();
+    const int t = blockIdx.x;
+    const int Q = nh * hd, KV = nkv * hd;
+    const float* row = qkv + (long long)t * (Q + 2 * KV);
+    const float pos = (float)positions[t];
+    const int half = inv_freq != nullptr ? rotary_dim / 2 : 0;
+    const int rd = 2 * half;
+    int in_page = 0, page = -1;
+    if (slots != nullptr) {
+        const int s = slots[t];
+        if (s >= 0) {
+            page = s / page_size;
+            in_page = s % page_size;
+            if (page >= total_pages) {
+                if (threadIdx.x == 0) *err = 2;
+                page = -1;
+            }
+        }
+    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        sc[i] = sn;
+        sc[half + i] = cs;
+    }
+    __syncthreads();
+    const int rot_heads = nh + nkv;
+    const int tpt = blockDim.x * gridDim.y, tid0 = blockIdx.y * blockDim.x + threadIdx.x;
+    // where head h of this token goes: a q row, or a k row of the cache (nullptr: not stored)
+    auto dst_of = [&](int h) -> T* {
+        if (h < nh) return q_out + (long long)t * Q + (long long)h * hd;
+        if (page < 0) return nullptr;
+        return k_cache + (((long long)page * nkv + (h - nh)) * page_size + in_page) * hd;
+    };
+    const int hq = half / 4;
+    for (int idx = tid0; idx < rot_heads * hq; idx += tpt) {
+        const int h = idx / hq, i = (idx % hq) * 4;
+        T* o = dst_of(h);
+        if (o == nullptr) continue;
+        const float* src = row + (long long)h * hd;
+        const float4 a = *reinterpret_cast<const float4*>(src + i), b = *reinterpret_cast<const float4*>(src + i + half);
+        const float4 sn = *reinterpret_cast<const float4*>(sc + i), cs = *reinterpret_cast<const float4*>(sc + half + i);
+        Out4<T>::store(o + i, a.x * cs.x - b.x * sn.x, a.y * cs.y - b.y * sn.y, a.z * cs.z - b.z * sn.z,
+                       a.w * cs.w - b.w * sn.w);
+        Out4<T>::store(o + i + half, a.x * sn.x + b.x * cs.x, a.y * sn.y + b.y * cs.y, a.z * sn.z + b.z * cs.z,
+                       a.w * sn.w + b.w * cs.w);
+    }
+    const int rq = (hd - rd) / 4;
+    for (int idx = tid0; idx < rot_heads * rq; idx += tpt) {
+        const int h = idx / rq, d = rd + (idx % rq) * 4;
+        T* o = dst_of(h);
+        if (o == nullptr) continue;
+        const float4 v = *reinterpret_cast<const float4*>(row + (long long)h * hd + d);
+        Out4<T>::store(o + d, v.x, v.y, v.z, v.w);
+    }
+    if (page >= 0) {
+        const float* vsrc = row + Q + KV;
+        for (int idx = tid0; idx < KV / 4; idx += tpt) {
+            const int kh = (idx * 4) / hd, d = (idx * 4) % hd;
+            const float4 v = *reinterpret_cast<const float4*>(vsrc + idx * 4);
+            Out4<T>::store(v_cache + (((long long)page * nkv + kh) * page_size + in_page) * hd + d, v.x, v.y, v.z, v.w);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ row gather
 __global__ void gather_rows_kernel(const uint4* src, const int32_t* rows,
                                    uint4* out, int chunks) {
@@ -171,6 +307,7 @@ __global__ void gather_rows_kernel(const uint4* src, const int32_t* rows,
 }
 
 // ------------------------------------------------------------------ moe combine
+template <bool VEC>
 __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
                                    const float* wts, const float* shared,
                                    const float* gate, float* resid, int H, int k) {
@@ -178,6 +315,28 @@ __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
     dep_launch_next();
     const int t = blockIdx.x;
     float* r = resid + (long long)t * H;
+    if (VEC) {
+        // four columns a thread; per element the same sums in the same order as below
+        const float g = (shared != nullptr && gate != nullptr) ? gate[t] : 1.0f;
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H / 4; i += blockDim.x * gridDim.y) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < k; ++j) {
+                const float wj = wts[t * k + j];
+                const float4 v = *reinterpret_cast<const float4*>(y + (long long)dest[t * k + j] * H + 4 * i);
+                acc.x = fmaf(wj, v.x, acc.x); acc.y = fmaf(wj, v.y, acc.y);
+                acc.z = fmaf(wj, v.z, acc.z); acc.w = fmaf(wj, v.w, acc.w);
+            }
+            if (shared != nullptr) {
+                const float4 v = *reinterpret_cast<const float4*>(shared + (long long)t * H + 4 * i);
+                acc.x = fmaf(g, v.x, acc.x); acc.y = fmaf(g, v.y, acc.y);
+                acc.z = fmaf(g, v.z, acc.z); acc.w = fmaf(g, v.w, acc.w);
+            }
+            float4 cur = *reinterpret_cast<float4*>(r + 4 * i);
+            cur.x += acc.x; cur.y += acc.y; cur.z += acc.z; cur.w += acc.w;
+            *reinterpret_cast<float4*>(r + 4 * i) = cur;
+        }
+        return;
+    }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += blockDim.x * gridDim.y) {
         float acc = 0.f;
         for (int j = 0; j < k; ++j)
@@ -206,9 +365,22 @@ void embed(const int32_t* tokens, const void* table, float* out, int T, int H, i
 void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int n_rows, int H, float eps,
              int out_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    if (out_dtype == F32) launch_dep(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, static_cast<float*>(out), rows, H, eps);
-    else launch_dep(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, static_cast<__nv_bfloat16*>(out), rows, H, eps);
+    // few rows: the eight warps of a block share a row; many rows: a warp each, eight rows to a block
+    const bool wide = n_rows < 1024;
+    const int grid = wide ? n_rows : (n_rows + 7) / 8, threads = 256;
+    const bool vec = H % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+                                     reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+#define DLM_NORM(TOUT, VEC, WIDE)                                                                              \
+    launch_dep(rmsnorm_kernel<TOUT, VEC, WIDE>, grid, threads, 0, stream, x, w, static_cast<TOUT*>(out), rows, \
+               n_rows, H, eps)
+    if (out_dtype == F32) {
+        if (vec) { if (wide) DLM_NORM(float, true, true); else DLM_NORM(float, true, false); }
+        else { if (wide) DLM_NORM(float, false, true); else DLM_NORM(float, false, false); }
+    } else {
+        if (vec) { if (wide) DLM_NORM(__nv_bfloat16, true, true); else DLM_NORM(__nv_bfloat16, true, false); }
+        else { if (wide) DLM_NORM(__nv_bfloat16, false, true); else DLM_NORM(__nv_bfloat16, false, false); }
+    }
+#undef DLM_NORM
     check_launch("rmsnorm");
 }
 
@@ -223,16 +395,27 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
     const int work = (nh + nkv) * hd;
     int slices = (work + threads - 1) / threads;
     if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
-    dim3 grid(T, slices);
     const size_t smem = inv_freq != nullptr ? sizeof(float) * rotary_dim : 0;
-    if (dtype == F32)
-        launch_dep(rope_kv_write_kernel<float>, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
+    const int half = inv_freq != nullptr ? rotary_dim / 2 : 0;
+    const bool vec = hd % 4 == 0 && half % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                       reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+    if (vec) {
+        slices = (work / 4 + threads - 1) / threads;
+        if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
+    }
+    dim3 grid(T, slices);
+    if (dtype == F32) {
+        auto kern = vec ? rope_kv_write_vec_kernel<float> : rope_kv_write_kernel<float>;
+        launch_dep(kern, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), nh, nkv, hd,
             page_size, total_pages, err);
-    else
-        launch_dep(rope_kv_write_kernel<__nv_bfloat16>, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
+    } else {
+        auto kern = vec ? rope_kv_write_vec_kernel<__nv_bfloat16> : rope_kv_write_kernel<__nv_bfloat16>;
+        launch_dep(kern, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
+    }
     check_launch("rope_kv_write");
 }
 
@@ -249,9 +432,13 @@ void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, in
 void moe_combine(const float* y, const int32_t* dest, const float* wts, const float* shared, const float* gate,
                  float* resid, int T, int H, int k, cudaStream_t stream) {
     if (T <= 0) return;
-    int slices = (H + 255) / 256;
+    const bool vec = H % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(shared) |
+                                     reinterpret_cast<uintptr_t>(resid)) & 15) == 0;
+    const int cols = vec ? H / 4 : H;
+    int slices = (cols + 255) / 256;
     if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
-    launch_dep(moe_combine_kernel, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k);
+    if (vec) launch_dep(moe_combine_kernel<true>, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k);
+    else launch_dep(moe_combine_kernel<false>, dim3(T, slices), 256, 0, stream, y, dest, wts, shared, gate, resid, H, k);
     check_launch("moe_combine");
 }
 

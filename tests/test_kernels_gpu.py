@@ -62,6 +62,16 @@ def test_rmsnorm(ops, ref, dtype, H):
     close(ops.rmsnorm(x, w, 3e-6, dtype, rows), ref.rmsnorm(x, w, 3e-6, dtype, rows), **tol(dtype))
 
 
+@pytest.mark.parametrize("H", [72, 1000, 2048])
+def test_rmsnorm_row_does_not_depend_on_the_batch(ops, H):
+    # few rows take the kernel with a block per row, many rows the one with a warp per row: same bits
+    x = rand((1500, H), torch.float32, 7, 2.0)
+    w = 1 + rand((H,), torch.float32, 8, 0.1)
+    many = ops.rmsnorm(x, w, 1e-6, torch.float32)
+    few = ops.rmsnorm(x[:6].contiguous(), w, 1e-6, torch.float32)
+    assert torch.equal(many[:6], few)
+
+
 def test_rmsnorm_hand_value(ops):
     # src/forward/cpu.rs:1289-1293: rmsnorm([3, 4], eps = 0) = [0.848528, 1.131371]
     x = torch.tensor([[3.0, 4.0]], device="cuda")
