@@ -21,6 +21,17 @@ void attention_prefill(const void* q, const void* k_cache, const void* v_cache, 
                        int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
                        cudaStream_t stream);
 
+// The same on the fifth-generation tensor cores (tcgen05, TMA): head size 128, pages of a power of two of at
+// least 64 tokens.  attention_prefill_tc returns false when the tensor maps cannot be made (the caller then
+// takes another kernel).  Off with DLM_B200_NO_TCGEN05=1.
+bool attention_prefill_tc_enabled();
+bool attention_prefill_tc_ok(const void* q, const void* k_cache, const void* v_cache, int nh, int nkv, int hd,
+                             int page_size);
+bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                          int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
+                          int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,
+                          cudaStream_t stream);
+
 // Split-key decode kernel for requests with exactly one query token (bfloat16 and float32).
 bool attention_decode_ok(int hd);
 void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk);

@@ -248,6 +248,9 @@ ATT_CASES = [
     (8, 4, 32, 64, 16, [(200, 17), (16, 16), (17, 17), (129, 1)]),
     (16, 16, 128, 64, 0, [(300, 40), (1024, 1), (65, 65)]),
     (14, 2, 128, 32, 0, [(257, 1), (90, 90)]),
+    (4, 2, 128, 64, 0, [(700, 700), (130, 2), (64, 64), (391, 129)]),
+    (2, 2, 128, 64, 100, [(600, 600), (300, 37), (1000, 255)]),
+    (3, 1, 128, 128, 0, [(513, 513), (129, 128)]),
     (2, 1, 256, 16, 0, [(50, 50), (33, 1)]),
     (4, 4, 80, 16, 40, [(130, 130)]),
 ]
