@@ -30,7 +30,7 @@ void attention(const void* q, const void* k_cache, const void* v_cache, const in
     }
     if (!decode || num_single < R) {
         if (fast && dtype == BF16 && attention_prefill_tc_enabled() &&
-            attention_prefill_tc_ok(q, k_cache, v_cache, nh, nkv, hd, page_size) &&
+            attention_prefill_tc_ok(q, k_cache, v_cache, nh, nkv, hd, page_size, scale) &&
             attention_prefill_tc(q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, out, T, R, nh, nkv, hd,
                                  page_size, total_pages, window, scale, decode ? 1 : 0, stream)) {
             // done on the tcgen05 path

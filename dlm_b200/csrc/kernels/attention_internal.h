@@ -26,7 +26,7 @@ void attention_prefill(const void* q, const void* k_cache, const void* v_cache, 
 // takes another kernel).  Off with DLM_B200_NO_TCGEN05=1.
 bool attention_prefill_tc_enabled();
 bool attention_prefill_tc_ok(const void* q, const void* k_cache, const void* v_cache, int nh, int nkv, int hd,
-                             int page_size);
+                             int page_size, float scale);
 bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
                           int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int T, int R, int nh,
                           int nkv, int hd, int page_size, int total_pages, int window, float scale, int skip_single,

@@ -2,18 +2,19 @@
 // multiple of 64 tokens: portions of prompts, each query attending to its request's paged keys up to its
 // own position (optionally only the last `window` of them).
 //
-// One block = 128 consecutive query tokens of one request x one query head.  Six warps, three roles:
-//   warp 4 (one lane)  the producer: the query tile once, then per tile of 128 keys the keys and the values
-//                      (TMA boxes of 64 keys x 64 dims straight from the pages, 128-byte swizzle), two tiles
-//                      in flight;
+// One block = 128 consecutive query tokens of one request x one query head.  Seven warps, three roles:
+//   warps 4 and 6      the producers (one lane each): the query tile once, then per tile of 128 keys the keys
+//                      (warp 4) and the values (warp 6), as TMA boxes of 64 keys x 64 dims straight from the
+//                      pages, 128-byte swizzle, two tiles of each in flight;
 //   warp 5 (one lane)  the MMA issuer: S = Q K^T (128 x 128, K-major operands) into one of two score buffers
 //                      in tensor memory, and O += P V (V is read as it lies in the cache: keys x dims, i.e.
 //                      MN-major) into the output accumulator in tensor memory; the scores of tile j + 1 are
 //                      issued before P V of tile j, so the tensor cores work while the softmax runs;
 //   warps 0-3          the softmax: thread i owns query row i = lane i of tensor memory.  It reads its scores
 //                      with tcgen05.ld, keeps the running maximum and sum in 32-bit, rescales its row of O in
-//                      tensor memory when the maximum moved, and writes P (bfloat16) into shared memory in the
-//                      layout the next MMA reads.  At the end it reads O, divides and stores.
+//                      tensor memory when the maximum moved far, and writes P (bfloat16) into one of two buffers
+//                      in shared memory in the layout the next MMA reads, so that it need not wait for the
+//                      product of the tile before.  At the end it reads O, divides and stores.
 // Every wait on a barrier is bounded (see tcgen05.cuh); a wait that runs out ends the block with error 5.
 //
 // Keys a query must not see (later positions, positions outside the window) get probability exactly 0.
@@ -33,7 +34,7 @@ namespace {
 using namespace tc5;
 
 constexpr int BQ = 128, BKV = 128, HD = 128;
-constexpr int SOFTMAX_WARPS = 4, PRODUCER_WARP = 4, MMA_WARP = 5, THREADS = 192;
+constexpr int SOFTMAX_WARPS = 4, KEY_WARP = 4, MMA_WARP = 5, VALUE_WARP = 6, THREADS = 224;
 constexpr uint32_t HALF_BYTES = 128 * 128;             // 128 rows x 64 elements: one swizzled half of a tile
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;        // 128 rows x 128 elements
 constexpr uint32_t TMEM_COLS = 512;                    // S0 | S1 | O | unused, 128 columns each
@@ -69,6 +70,27 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// tcgen05.ld without its wait, and the wait as a statement that the registers depend on (so that no use of them
+// can be placed before it)
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+          "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+          "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+          "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+        :: "memory");
+}
 // MN-major operand tile with 128-byte swizzle (the contiguous dimension is the MMA's N): rows are K, 128 bytes
 // each, groups of 8 rows 1024 bytes apart; the next 64 elements of N lie `n_block_bytes` further.
 __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t n_block_bytes) {
@@ -85,7 +107,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_free[2], p_ready, pv_done;
+    __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], s_full[2], s_free[2], p_ready[2], pv_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
     __shared__ int s_map[2];
@@ -96,7 +118,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* Qs = base;                              // [2 halves][128 queries][128 bytes]
     unsigned char* Ks = Qs + TILE_BYTES;                   // [2 stages][2 halves][128 keys][128 bytes]
     unsigned char* Vs = Ks + 2 * TILE_BYTES;               // [2 stages][2 halves][128 keys][128 bytes]
-    unsigned char* Ps = Vs + 2 * TILE_BYTES;               // [2 halves of the keys][128 queries][128 bytes]
+    unsigned char* Ps = Vs + 2 * TILE_BYTES;               // [2 buffers][2 halves of the keys][128 queries][128 bytes]
 
     // work item: blocks start in the order of their linear index; the latest query tiles (most keys) go first
     const int linear = (int)(blockIdx.y * gridDim.x + blockIdx.x);
@@ -118,13 +140,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         mbar_init(&q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
+            mbar_init(&k_full[s], 1);
+            mbar_init(&v_full[s], 1);
             mbar_init(&s_full[s], 1);
             mbar_init(&s_free[s], SOFTMAX_WARPS * 32);
+            mbar_init(&p_ready[s], SOFTMAX_WARPS * 32);
+            mbar_init(&pv_done[s], 1);
         }
-        mbar_init(&p_ready, SOFTMAX_WARPS * 32);
-        mbar_init(&pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -151,17 +173,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int t_begin = (lo / BKV) * BKV;
     const int n_tiles = (hi - t_begin) / BKV + 1;
 
-    if (warp == PRODUCER_WARP) {
+    if (warp == KEY_WARP || warp == VALUE_WARP) {
+        // one warp brings the queries and the keys, another the values: a key stage is free as soon as its scores
+        // are computed (s_full), a value stage only after its P V product (pv_done), and neither copy waits for
+        // the other
         if (lane == 0) {
+            const bool keys = warp == KEY_WARP;
             const int32_t* table = p.block_table + (long long)r * p.table_width;
             const int rows_total = p.total_pages * p.nkv * p.page_size;
-            mbar_expect_tx(&q_full, TILE_BYTES);
-            tma_load_2d(Qs, &map_q, head * HD, q_begin + q0, &q_full);
-            tma_load_2d(Qs + HALF_BYTES, &map_q, head * HD + 64, q_begin + q0, &q_full);
+            const CUtensorMap* map = keys ? &map_k : &map_v;
+            uint64_t* full = keys ? k_full : v_full;
+            uint64_t* empty = keys ? s_full : pv_done;
+            unsigned char* tiles = keys ? Ks : Vs;
+            if (keys) {
+                mbar_expect_tx(&q_full, TILE_BYTES);
+                tma_load_2d(Qs, &map_q, head * HD, q_begin + q0, &q_full);
+                tma_load_2d(Qs + HALF_BYTES, &map_q, head * HD + 64, q_begin + q0, &q_full);
+            }
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j & 1;
-                if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) break;
-                mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+                if (j >= 2 && !mbar_wait(&empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+                mbar_expect_tx(&full[s], TILE_BYTES);
                 const int j0 = t_begin + j * BKV;
 #pragma unroll
                 for (int part = 0; part < 2; ++part) {               // two runs of 64 keys
@@ -173,12 +205,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (page < 0 && key0 <= hi && key0 + 63 >= lo) *p.err = 3;
                     // a run without a page is read from outside the tensor: zeros
                     const int y = page >= 0 ? (page * p.nkv + kvh) * p.page_size + (key0 & (p.page_size - 1)) : rows_total;
-                    unsigned char* kd = Ks + (size_t)s * TILE_BYTES + part * (64 * 128);
-                    unsigned char* vd = Vs + (size_t)s * TILE_BYTES + part * (64 * 128);
-                    tma_load_2d(kd, &map_k, 0, y, &kv_full[s]);
-                    tma_load_2d(kd + HALF_BYTES, &map_k, 64, y, &kv_full[s]);
-                    tma_load_2d(vd, &map_v, 0, y, &kv_full[s]);
-                    tma_load_2d(vd + HALF_BYTES, &map_v, 64, y, &kv_full[s]);
+                    unsigned char* dst = tiles + (size_t)s * TILE_BYTES + part * (64 * 128);
+                    tma_load_2d(dst, map, 0, y, &full[s]);
+                    tma_load_2d(dst + HALF_BYTES, map, 64, y, &full[s]);
                 }
             }
         }
@@ -188,18 +217,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) |
                                          ((uint32_t)(BQ >> 4) << 24);
             constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);          // B (the values) is MN-major
-            const uint32_t q_addr = smem_u32(Qs), p_addr = smem_u32(Ps);
+            // operand descriptors of every buffer, made once: a step of 16 along K adds a constant to the
+            // address field (in units of 16 bytes)
+            const uint64_t dq = umma_desc(smem_u32(Qs));
+            const uint64_t dk[2] = {umma_desc(smem_u32(Ks)), umma_desc(smem_u32(Ks + TILE_BYTES))};
+            const uint64_t dp[2] = {umma_desc(smem_u32(Ps)), umma_desc(smem_u32(Ps + TILE_BYTES))};
+            const uint64_t dv[2] = {umma_desc_mn(smem_u32(Vs), HALF_BYTES), umma_desc_mn(smem_u32(Vs + TILE_BYTES), HALF_BYTES)};
             auto issue_s = [&](int j) {
-                const uint32_t k_addr = smem_u32(Ks + (size_t)(j & 1) * TILE_BYTES);
+                const uint64_t dkj = dk[j & 1];
                 const uint32_t d_tmem = tmem_base + (uint32_t)(j & 1) * BKV;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-                    umma_bf16(d_tmem, umma_desc(q_addr + off), umma_desc(k_addr + off), IDESC_S, kk > 0 ? 1u : 0u);
+                    const uint64_t off = (uint64_t)((kk >> 2) * (HALF_BYTES >> 4) + (kk & 3) * 2);
+                    umma_bf16(d_tmem, dq + off, dkj + off, IDESC_S, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[j & 1]);
+                umma_commit(&s_full[j & 1]);         // the scores are there, and the keys of the stage are read
             };
-            bool ok = mbar_wait(&q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
+            bool ok = mbar_wait(&q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 issue_s(0);
@@ -207,24 +241,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) {
                     const int s = (j + 1) & 1;
-                    if (!mbar_wait(&kv_full[s], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&k_full[s], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                     // the softmax of tile j - 1 has read this score buffer
                     if (j + 1 >= 2 && !mbar_wait(&s_free[s], (((j + 1) >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(j + 1);
                 }
-                if (!mbar_wait(&p_ready, j & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&p_ready[j & 1], (j >> 1) & 1, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = smem_u32(Vs + (size_t)(j & 1) * TILE_BYTES);
+                const uint64_t dpj = dp[j & 1], dvj = dv[j & 1];
                 const uint32_t o_tmem = tmem_base + 2 * BKV;
+                const uint32_t first = j > 0 ? 1u : 0u;
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; ++kk) {
-                    const uint64_t da = umma_desc(p_addr + (kk >> 2) * HALF_BYTES + (kk & 3) * 32);
-                    const uint64_t db = umma_desc_mn(v_addr + kk * (16 * 128), HALF_BYTES);
-                    umma_bf16(o_tmem, da, db, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+                    const uint64_t da = dpj + (uint64_t)((kk >> 2) * (HALF_BYTES >> 4) + (kk & 3) * 2);
+                    const uint64_t db = dvj + (uint64_t)(kk * (16 * 128 >> 4));          // 16 keys further
+                    umma_bf16(o_tmem, da, db, IDESC_PV, kk > 0 ? 1u : first);
                 }
-                umma_commit(&kv_empty[j & 1]);       // keys and values of the stage are read
-                umma_commit(&pv_done);               // O holds tiles 0..j; P may be written again
+                // O holds tiles 0..j; this P buffer may be written again; the values of the stage are read
+                umma_commit(&pv_done[j & 1]);
             }
         }
     } else {
@@ -233,7 +269,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = pos0 + row;
         const uint32_t lane_base = ((uint32_t)(warp * 32) << 16);
         const uint32_t o_tmem = tmem_base + 2 * BKV + lane_base;
-        unsigned char* p_row = Ps + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
+        unsigned char* p_row0 = Ps + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
+        // m is the maximum the probabilities are taken against.  It follows the row's true maximum only when
+        // that has grown by more than 2^RESCALE_STEP since (or at the row's first keys): a probability is then
+        // at most 2^RESCALE_STEP instead of 1, which neither bfloat16 nor the 32-bit sums mind, the final
+        // division makes up for it exactly, and O is seldom rescaled.
+        constexpr float RESCALE_STEP = 8.0f;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
@@ -242,65 +283,71 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // (the outcome of a wait is made the same for the whole warp: the collectives below need all lanes)
             if (!__all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the row's 128 scores
+            uint32_t v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32_issue(s_tmem + (uint32_t)(c * 32), v[c]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_fence(v[c]);
+            // the scores are in registers: the buffer may take the scores of the tile after the next
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&s_free[j & 1]);
             // does every row of this warp see every key of the tile?  Then nothing is masked.
             const bool row_all = j0 + BKV - 1 <= pos && (p.window <= 0 || pos - j0 < p.window);
             const bool warp_all = __all_sync(0xffffffffu, row_all);
-            // pass 1: the row's maximum (scores scaled to base 2)
-            float mx = m;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(s_tmem + (uint32_t)(c * 32), v);
-                if (warp_all) {
+            if (!warp_all) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
-                } else {
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = j0 + c * 32 + i;
                         const bool vis = key <= pos && (p.window <= 0 || pos - key < p.window);
-                        if (vis) mx = fmaxf(mx, __uint_as_float(v[i]) * p.scale_log2);
+                        if (!vis) v[c][i] = 0xff800000u;             // -inf
                     }
+            }
+            // the row's maximum of the raw scores (the scale is positive), four chains
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[c][i]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;   // -inf: nothing seen
+            float alpha = 1.0f;
+            if (mx > m + RESCALE_STEP || m == -INFINITY) {
+                if (mx != -INFINITY) {
+                    alpha = ex2(m - mx);                                // m = -inf: 0
+                    m = mx;
                 }
             }
-            // a row that has seen nothing yet keeps its state (2^(-inf - -inf) must not appear)
-            const float base_m = mx == -INFINITY ? 0.f : mx;
-            const float alpha = ex2(m - base_m);                   // m = -inf: 0
-            // P V of the tile before this one must be done before O is rescaled and P is overwritten
-            if (j > 0) {
-                if (!__all_sync(0xffffffffu, mbar_wait(&pv_done, (j - 1) & 1, abort_flag))) { ok = false; break; }
+            const float base_m = m == -INFINITY ? 0.f : m;               // nothing seen yet: every probability is 0
+            // O is rescaled only between two P V products: the one of the tile before this must be done
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                {
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(o_tmem + (uint32_t)(c * 32), v);
+                        uint32_t o[32];
+                        tmem_ld32(o_tmem + (uint32_t)(c * 32), o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(o_tmem + (uint32_t)(c * 32), v);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(o_tmem + (uint32_t)(c * 32), o);
                     }
                 }
             }
-            // pass 2: probabilities, their sum, P in bfloat16 into shared memory (K-major, 128-byte swizzle)
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(s_tmem + (uint32_t)(c * 32), v);
+            // this P buffer was read by the P V product of two tiles ago
+            if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&pv_done[j & 1], ((j >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
+            unsigned char* p_row = p_row0 + (size_t)(j & 1) * TILE_BYTES;
+            // probabilities, their sum (four chains), P in bfloat16 into shared memory (K-major, 128-byte swizzle)
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 float pr[32];
-                if (warp_all) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) pr[i] = ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -base_m));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = j0 + c * 32 + i;
-                        const bool vis = key <= pos && (p.window <= 0 || pos - key < p.window);
-                        pr[i] = vis ? ex2(fmaf(__uint_as_float(v[i]), p.scale_log2, -base_m)) : 0.f;
-                    }
+                for (int i = 0; i < 32; ++i) {
+                    pr[i] = ex2(fmaf(__uint_as_float(v[c][i]), p.scale_log2, -base_m));     // -inf: 0
+                    sum4[i & 3] += pr[i];
                 }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sum += pr[i];
                 // keys 32c .. 32c + 31 of this row: half c / 2, 16-byte chunks 4 (c % 2) .. + 3 of the row
                 unsigned char* dst = p_row + (size_t)(c >> 1) * HALF_BYTES;
 #pragma unroll
@@ -314,15 +361,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     *reinterpret_cast<uint4*>(dst + ((chunk ^ (row & 7)) << 4)) = w;
                 }
             }
-            l = l * alpha + sum;
-            m = mx;
-            // the scores are read, P and O are written: hand over to the MMA issuer
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // P and O are written: hand over to the MMA issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(&s_free[j & 1]);
-            mbar_arrive(&p_ready);
+            mbar_arrive(&p_ready[j & 1]);
         }
-        if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done, (n_tiles - 1) & 1, abort_flag))) {
+        if (ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag))) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const int Q = p.nh * HD;
@@ -387,8 +432,9 @@ bool attention_prefill_tc_enabled() {
 }
 
 bool attention_prefill_tc_ok(const void* q, const void* k_cache, const void* v_cache, int nh, int nkv, int hd,
-                             int page_size) {
-    return hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
+                             int page_size, float scale) {
+    // (the row maximum is taken before the scores are scaled: the scale must be positive)
+    return scale > 0.f && hd == HD && nkv > 0 && nh % nkv == 0 && page_size >= 64 && (page_size & (page_size - 1)) == 0 &&
            ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
              reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
 }
@@ -407,7 +453,7 @@ bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cach
     while ((1 << shift) < page_size) ++shift;
     PrefillTcParams p{block_table, table_width, cu_q, kv_len, static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size,
                       shift, total_pages, window, scale * 1.4426950408889634f, skip_single, error_flag_ptr()};
-    const size_t smem = (size_t)TILE_BYTES * 6 + 1024;      // Q, 2 x K, 2 x V, P, and room to align
+    const size_t smem = (size_t)TILE_BYTES * 7 + 1024;      // Q, 2 x K, 2 x V, 2 x P, and room to align
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(nh, (T + BQ - 1) / BQ + R);
     attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
