@@ -222,6 +222,29 @@ def test_rope_identity_at_zero_and_norm(ops):
     close(q[1].view(nh, hd).norm(dim=-1), qkv[1, :nh * hd].view(nh, hd).norm(dim=-1), rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("E,H,I,counts", [
+    (6, 2048 + 512, 96, [40, 0, 1, 0, 3, 2]),      # one expert far above the mean: several passes over its rows
+    (4, 5632, 64, [0, 17, 0, 5]),                  # rows longer than one stage: chunks of K
+    (3, 264, 1408, [9, 9, 9]),
+])
+def test_grouped_products_skewed(ops, ref, E, H, I, counts):
+    """Few rows in all, very unevenly spread: the weight-streaming kernel takes an expert's rows in passes."""
+    dtype = torch.bfloat16
+    M = sum(counts)
+    offsets = torch.tensor([0] + torch.tensor(counts).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    g = torch.Generator().manual_seed(5)
+    T = 23
+    h = rand((T, H), dtype, 14)
+    rows = torch.randint(0, T, (M,), generator=g).to(torch.int32).cuda()
+    w_gu = rand((E, 2 * I, H), dtype, 15, 0.05)
+    w_d = rand((E, H, I), dtype, 16, 0.05)
+    act = ops.grouped_swiglu(h, w_gu, offsets, rows)
+    close(act, ref.grouped_swiglu(h, w_gu, offsets, rows), **tol(dtype, H))
+    y = ops.grouped_linear(act, w_d, offsets)
+    close(y, ref.grouped_linear(act, w_d, offsets), **tol(torch.float32, I))
+    ops.check_errors()
+
+
 # ----------------------------------------------------------------------- attention
 def build_paged(reqs, nkv, hd, ps, dtype, seed, shuffle=True):
     """reqs: list of (kv_len, q_len).  Returns q, caches, table, cu_q, kv_len with pages scattered."""

@@ -21,10 +21,11 @@ TOL = {"float32": 1e-4, "bfloat16": 1e-2}
 MARGIN = {"float32": 1e-6, "bfloat16": 2e-4}
 
 
-def replay(folder, dtype, steps, out_dir, max_tokens):
+def replay(folder, dtype, steps, out_dir, max_tokens, env=None):
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens)]
-    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1,
+                            env=None if env is None else {**os.environ, **env})
     try:
         for st in steps:
             proc.stdin.write(json.dumps(st) + "\n")
@@ -90,3 +91,22 @@ def test_trace_run_mixed(name, dtype, tiny_folders, tmp_path):
         assert d <= TOL[dtype], f"{rid} position {p}: {d:.3e}"
         checked += 1
     assert checked > 0.5 * len(got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_launches_change_no_bit(dtype, tiny_folders, tmp_path):
+    """Kernels that start while the kernel before them ends, and the shared expert on a second stream, only
+    move work in time: with both switched off the same trace gives the same bits."""
+    name = "B"
+    V = TINY[name]["cfg"]["vocab_size"]
+    toks = {f"q{i}": prompt(300 + i, n, V) for i, n in enumerate([70, 33, 100, 16])}
+    steps, _ = cuttings.mixed(toks, max_live=4, seed=11)
+    peak = cuttings.peak_tokens(steps)
+    outs = []
+    for tag, env in (("on", None), ("off", {"DLM_B200_NO_PDL": "1", "DLM_B200_NO_BRANCH": "1"})):
+        out_dir = str(tmp_path / tag)
+        replay(tiny_folders[name], dtype, steps, out_dir, peak, env=env)
+        outs.append(read_logits(out_dir, steps, V))
+    assert outs[0].keys() == outs[1].keys() and outs[0]
+    for key in outs[0]:
+        assert torch.equal(outs[0][key], outs[1][key]), f"{key} differs"
