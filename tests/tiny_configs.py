@@ -1,7 +1,9 @@
 """Tiny Qwen2-MoE configurations for the tests.  A and B differ in every size and option
 (heads and groups, head size, widths that are no power of two, layers, vocabulary, eps,
 rope base, window, experts and top-k, renormalisation, dense layers, tied head); C adds
-an explicit head_dim that is not hidden/heads, a single kv head and no shared expert."""
+an explicit head_dim that is not hidden/heads, a single kv head and no shared expert; D has
+the head size (128) and widths (multiples of 8) that the tcgen05 attention and GEMM kernels take,
+so that the engine tests reach them with pages of 64 tokens and prompts above 128 tokens."""
 import torch
 
 TINY = {
@@ -26,6 +28,13 @@ TINY = {
         norm_topk_prob=True, decoder_sparse_step=1, intermediate_size=88,
         vocab_size=301, rope_theta=50000.0, rms_norm_eps=3e-6, use_sliding_window=True, sliding_window=24,
         max_window_layers=0, tie_word_embeddings=False)),
+    "D": dict(seed=3, cfg=dict(
+        architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe",
+        num_hidden_layers=2, hidden_size=192, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+        num_experts=6, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=128,
+        norm_topk_prob=False, decoder_sparse_step=1, intermediate_size=96,
+        vocab_size=520, rope_theta=20000.0, rms_norm_eps=2e-6, use_sliding_window=True, sliding_window=40,
+        max_window_layers=1, tie_word_embeddings=False)),
 }
 
 
