@@ -8,10 +8,11 @@ namespace dlmk {
 void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
           const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N, int K,
           int in_dtype, int out_dtype, int epilogue, int fast, cudaStream_t stream) {
-    // many rows: the tcgen05 kernel (rows of A must be contiguous)
+    // more rows than the weight-streaming kernel takes in one pass: the tcgen05 kernel (rows of A must be
+    // contiguous)
     if (fast && a_rows == nullptr && gemm_tc_enabled() &&
         gemm_tc_ok(a, lda, w, ldw, w_expert_stride, M, N, K, in_dtype) &&
-        ((expert_offsets == nullptr && M >= 128) ||
+        ((expert_offsets == nullptr && M > 16) ||
          (expert_offsets != nullptr && bias == nullptr && (long long)M > 16LL * num_experts))) {
         if (gemm_tc(a, lda, w, ldw, expert_offsets, num_experts, bias, out, ldo, M, N, K, out_dtype, epilogue, stream))
             return;
@@ -20,7 +21,7 @@ void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw,
         const bool stream_ok = gemm_stream_enabled() &&
             gemm_stream_ok(a, lda, w, ldw, w_expert_stride, expert_offsets, num_experts, M, N, K, in_dtype);
         if (expert_offsets == nullptr) {
-            if (M <= 64 && stream_ok) {
+            if (M <= 16 && stream_ok) {
                 gemm_stream(a, lda, a_rows, w, ldw, w_expert_stride, nullptr, 0, bias, out, ldo, M, N, K, out_dtype,
                             epilogue, M, stream);
                 return;

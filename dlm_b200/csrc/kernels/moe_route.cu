@@ -271,7 +271,8 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     const int rows = E + (has_gate ? 1 : 0);
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     const size_t smem_multi = sizeof(float) * (size_t)H * ROUTER_TB;
-    if (vec && T >= 32 && smem_multi <= 200 * 1024) {
+    // (with few tokens the one-token kernel has more blocks: tokens x groups of experts)
+    if (vec && T >= 512 && smem_multi <= 200 * 1024) {
         dim3 mgrid((T + ROUTER_TB - 1) / ROUTER_TB);
 #define DLM_ROUTER_MULTI(TX, TW)                                                                              \
     {                                                                                                         \
