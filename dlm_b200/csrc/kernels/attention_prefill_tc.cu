@@ -151,7 +151,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     __syncthreads();
     const int r = s_map[0];
-    if (r < 0) return;                                     // uniform over the block; nothing allocated yet
+    if (r < 0) {                                           // uniform over the block; nothing allocated yet
+        dep_wait();                                        // (every block waits for the kernel before, see common.cuh)
+        return;
+    }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                      "r"(TMEM_COLS) : "memory");
@@ -162,6 +165,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     volatile int* abort_flag = &s_abort;
+    // the set-up above may run while the kernel before this one ends (see dep_wait in common.cuh)
+    dep_wait();
+    dep_launch_next();
 
     const int q0 = s_map[1];
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin;
@@ -456,7 +462,7 @@ bool attention_prefill_tc(const void* q, const void* k_cache, const void* v_cach
     const size_t smem = (size_t)TILE_BYTES * 7 + 1024;      // Q, 2 x K, 2 x V, 2 x P, and room to align
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(nh, (T + BQ - 1) / BQ + R);
-    attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
+    launch_dep(attention_prefill_tc_kernel, grid, THREADS, smem, stream, mq, mk, mv, p);
     check_launch("attention_prefill_tc");
     return true;
 }

@@ -128,6 +128,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = tmem_slot;
     volatile int* abort_flag = &s_abort;
     const int k_tiles = (p.K + BK - 1) / BK;
+    // the set-up above may run while the kernel before this one ends (see dep_wait in common.cuh)
+    dep_wait();
+    dep_launch_next();
 
     if (warp == PRODUCER_WARP) {
         if (lane == 0) {
@@ -388,7 +391,7 @@ void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int n
     auto kern = gemm_tc_kernel<STAGES, G, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int grid = total_tiles < sm_count() ? total_tiles : sm_count();
-    kern<<<grid, THREADS, smem, stream>>>(mw, ma, p, nx, total_tiles);
+    launch_dep(kern, grid, THREADS, smem, stream, mw, ma, p, nx, total_tiles);
 }
 
 }  // namespace
