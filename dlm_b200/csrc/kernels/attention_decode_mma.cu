@@ -44,6 +44,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// How many blocks of a (request, kv head, pass of heads) have written their partial results: the block that
+// comes last merges them, so no second kernel is needed.  The counters are zero between launches (the last
+// block puts its counter back), so launches must not overlap; MERGE_SLOTS bounds requests x kv heads x passes.
+constexpr int MERGE_SLOTS = 1 << 16;
+__device__ int g_merge_counters[MERGE_SLOTS];
+
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache,
@@ -51,7 +57,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
                             int table_width, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ kv_len,
                             float* part_o, float* part_ml, int nh, int nkv, int page_size,
                             int page_shift, int total_pages, int window, float scale_log2, int chunk, int n_splits,
-                            int head_passes, int* err) {
+                            int head_passes, __nv_bfloat16* out, int fuse_merge, int* err) {
     constexpr int PITCH = HD + 8;
     constexpr int KS = HD / 16, DT = HD / 8, CPR = HD / 8;
     dep_wait();
@@ -253,13 +259,43 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* k_cache
         // the merge kernel works with natural-base maxima
         if (d == 0) { part_ml[base * 2] = mx * 0.6931471805599453f; part_ml[base * 2 + 1] = ls; }
     }
+    if (!fuse_merge) return;
+    // the last of this (request, kv head, pass)'s blocks merges all splits, with the merge kernel's arithmetic
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int slot = r * (int)gridDim.y + (int)blockIdx.y;
+        s_last = atomicAdd(&g_merge_counters[slot], 1) == n_splits - 1 ? 1 : 0;
+        if (s_last) g_merge_counters[slot] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < n_heads * HD; idx += WARPS * 32) {
+        const int row = idx / HD, d = idx % HD;
+        const long long base = ((long long)r * nh + (h0 + row)) * n_splits;
+        float mx = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, __ldcg(part_ml + (base + s) * 2));
+        float acc = 0.f, ls = 0.f;
+        if (mx != -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const float ms = __ldcg(part_ml + (base + s) * 2);
+                if (ms == -INFINITY) continue;
+                const float a = expf(ms - mx);
+                acc = fmaf(a, __ldcg(part_o + (base + s) * HD + d), acc);
+                ls = fmaf(a, __ldcg(part_ml + (base + s) * 2 + 1), ls);
+            }
+        }
+        out[(long long)token * nh * HD + (long long)(h0 + row) * HD + d] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
+    }
 }
 
 template <int HD>
 void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
             const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, float* part_o,
             float* part_ml, int nh, int nkv, int page_size, int total_pages, int window, float scale, int chunk,
-            int n_splits, int head_passes) {
+            int n_splits, int head_passes, void* out, int fuse_merge) {
     size_t smem = (size_t)(ROWS + 4 * BKV) * (HD + 8) * sizeof(__nv_bfloat16);
     const size_t merge = sizeof(float) * (size_t)(2 * WARPS * ROWS + WARPS * ROWS * HD);
     if (merge > smem) smem = merge;
@@ -271,7 +307,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv,
         page_size, shift, total_pages, window, scale * 1.4426950408889634f, chunk, n_splits, head_passes,
-        error_flag_ptr());
+        static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr());
 }
 
 }  // namespace
@@ -288,9 +324,10 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)R * nh * n_splits * hd;
     dim3 grid(R, nkv * head_passes, n_splits);
+    const int fuse_merge = (long long)R * nkv * head_passes <= MERGE_SLOTS ? 1 : 0;
 #define DLM_DECODE(HD)                                                                                              \
     launch<HD>(grid, stream, q, k_cache, v_cache, block_table, table_width, cu_q, kv_len, part_o, part_ml, nh, nkv, \
-               page_size, total_pages, window, scale, chunk, n_splits, head_passes)
+               page_size, total_pages, window, scale, chunk, n_splits, head_passes, out, fuse_merge)
     switch (hd) {
         case 16: DLM_DECODE(16); break;
         case 32: DLM_DECODE(32); break;
@@ -301,7 +338,7 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
     }
 #undef DLM_DECODE
     check_launch("attention_decode_mma");
-    attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, n_splits, BF16, stream);
+    if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, n_splits, BF16, stream);
 }
 
 }  // namespace dlmk

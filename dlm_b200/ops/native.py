@@ -190,7 +190,9 @@ class NativeOps:
             n = self.k.attention_scratch_floats(R, nh, nkv, hd, int(max_kv_len))
             if n > 0:
                 scratch = torch.empty((n,), dtype=torch.float32, device=q.device)
-        self.launches += 1 if scratch is None else (2 if num_single == R else 3)
+        # the tensor-core decode kernel merges its key splits itself; the FMA one has a merge kernel behind it
+        decode_kernels = 1 if (q.dtype == torch.bfloat16 and hd in (16, 32, 48, 64, 96, 128)) else 2
+        self.launches += 1 if scratch is None else (decode_kernels if num_single == R else decode_kernels + 1)
         self.k.attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), width, _p(cu_q), _p(kv_len), _p(out), T, R,
                          nh, nkv, hd, page_size, total_pages, int(window), float(scale), int(max_q_len),
                          int(max_kv_len), int(num_single), _p(scratch), _dt(q.dtype), self.fast, self._stream())
