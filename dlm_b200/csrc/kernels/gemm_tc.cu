@@ -87,9 +87,9 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty) {
 
 // Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulators in tensor memory
 // alternate, so that the epilogue of one tile runs while the MMAs of the next are issued.
-// Token tiles are fetched with the smallest of eight boxes (32, 64, ..., 256 rows) that holds the tile's tokens,
+// Token tiles are fetched with the smallest of sixteen boxes (16, 32, ..., 256 rows) that holds the tile's tokens,
 // so that a short group does not cost the bandwidth of a full one.
-struct TokenMaps { CUtensorMap m[8]; };
+struct TokenMaps { CUtensorMap m[16]; };
 
 template <int STAGES, int G, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
@@ -105,6 +105,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __shared__ __align__(8) uint64_t acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
+    // the block's first tiles, looked up once (the search through the experts' offsets is too slow to stand at
+    // the head of every tile in every role)
+    constexpr int TABLE = 64;
+    __shared__ TileInfo s_tiles[TABLE];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -117,6 +121,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPI_WARPS * 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (int i = tid; i < TABLE; i += THREADS) {
+        const long long tile = (long long)blockIdx.x + (long long)i * gridDim.x;
+        if (tile < total_tiles) s_tiles[i] = tile_info(p, (int)(tile / nx));
+    }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                      "r"((uint32_t)(2 * TT)) : "memory");
@@ -128,6 +136,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = tmem_slot;
     volatile int* abort_flag = &s_abort;
     const int k_tiles = (p.K + BK - 1) / BK;
+    auto info_of = [&](int tile) -> TileInfo {
+        const int i = (tile - (int)blockIdx.x) / (int)gridDim.x;
+        return i < TABLE ? s_tiles[i] : tile_info(p, tile / nx);
+    };
     // the set-up above may run while the kernel before this one ends (see dep_wait in common.cuh)
     dep_wait();
     dep_launch_next();
@@ -137,13 +149,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t it = 0;                                  // slices issued so far, over all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileInfo ti = tile_info(p, tile / nx);
+                const TileInfo ti = info_of(tile);
                 if (ti.expert < 0) continue;
                 const int n0 = (tile % nx) * (G * BM);
                 const int n_w = min(G, (p.N - n0 + BM - 1) / BM);     // weight tiles of this item
                 const int n_tok = ti.row_end - ti.row_begin;
-                const int bi = (n_tok + 31) / 32 - 1;         // box of 32 * (bi + 1) rows
-                const int box = 32 * (bi + 1);
+                const int bi = (n_tok + 15) / 16 - 1;         // box of 16 * (bi + 1) rows
+                const int box = 16 * (bi + 1);
                 const CUtensorMap* map_a = &maps_a.m[bi];
                 const uint32_t tx = (uint32_t)n_w * W_BYTES + (uint32_t)box * BK * 2;
                 const int w_row = (p.expert_offsets != nullptr ? ti.expert * p.N : 0) + n0;
@@ -163,7 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t it = 0, acc_i = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const TileInfo ti = tile_info(p, tile / nx);
+                const TileInfo ti = info_of(tile);
                 if (ti.expert < 0) continue;
                 const int n_mma = max(16, (ti.row_end - ti.row_begin + 15) & ~15);
                 const uint32_t idesc = IDESC0 | ((uint32_t)(n_mma >> 3) << 17);
@@ -205,7 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             TileInfo ti;
-            if (lane == 0) ti = tile_info(p, tile / nx);
+            if (lane == 0) ti = info_of(tile);
             ti.expert = __shfl_sync(0xffffffffu, ti.expert, 0);
             ti.row_begin = __shfl_sync(0xffffffffu, ti.row_begin, 0);
             ti.row_end = __shfl_sync(0xffffffffu, ti.row_end, 0);
@@ -424,8 +436,8 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     TokenMaps ma;
     const long long w_rows = expert_offsets ? (long long)num_experts * N : N;
     if (!make_map(&mw, w, w_rows, K, ldw, BM)) return false;
-    for (int i = 0; i < 8; ++i)
-        if (!make_map(&ma.m[i], a, M, K, lda, 32 * (i + 1))) return false;
+    for (int i = 0; i < 16; ++i)
+        if (!make_map(&ma.m[i], a, M, K, lda, 16 * (i + 1))) return false;
     TcParams p{expert_offsets, num_experts, bias, out, ldo, M, N, K, error_flag_ptr()};
     int t_tiles = (M + TT - 1) / TT;
     if (expert_offsets != nullptr) t_tiles += num_experts;
