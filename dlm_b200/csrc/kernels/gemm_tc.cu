@@ -373,7 +373,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // ----------------------------------------------------------------------------- host side
 // rows x K bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64 elements, 128-byte swizzle,
 // elements outside the matrix read as zero
-bool make_map(CUtensorMap* map, const void* base, long long rows, int K, int ld, int box_rows) {
+bool make_map(CUtensorMap* map, const void* base, long long rows, int K, int ld, int box_rows,
+              CUtensorMapL2promotion promote = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
     EncodeTiledFn fn = encode_tiled();
     if (fn == nullptr) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -381,7 +382,7 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, int K, int ld,
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promote,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -435,7 +436,8 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     CUtensorMap mw;
     TokenMaps ma;
     const long long w_rows = expert_offsets ? (long long)num_experts * N : N;
-    if (!make_map(&mw, w, w_rows, K, ldw, BM)) return false;
+    // (weights: a miss fetches 256 bytes of the row, i.e. the next slice's box too)
+    if (!make_map(&mw, w, w_rows, K, ldw, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return false;
     for (int i = 0; i < 16; ++i)
         if (!make_map(&ma.m[i], a, M, K, lda, 16 * (i + 1))) return false;
     TcParams p{expert_offsets, num_experts, bias, out, ldo, M, N, K, error_flag_ptr()};
