@@ -174,6 +174,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0, acc_i = 0;
             bool ok = true;
+            // descriptor of stage 0's weight tile; a stage, a weight tile or the token tile further on is a constant
+            // added to the address field (in units of 16 bytes): the issuing thread has little else to do per stage
+            const uint64_t dw0 = umma_desc(smem_u32(tiles));
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const TileInfo ti = info_of(tile);
                 if (ti.expert < 0) continue;
@@ -190,10 +193,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const uint32_t s = it % STAGES;
                     if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t w_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                    const uint64_t da = umma_desc(w_addr + G * W_BYTES);
+                    const uint64_t ds = dw0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+                    const uint64_t da = ds + (uint64_t)(G * (W_BYTES >> 4));
                     for (int t = 0; t < n_w; ++t) {
-                        const uint64_t dw = umma_desc(w_addr + t * W_BYTES);
+                        const uint64_t dw = ds + (uint64_t)(t * (W_BYTES >> 4));
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)      // 16 elements of K = 32 bytes = 2 address units
                             umma_bf16(d_tmem + t * TT, dw + 2 * k, da + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
