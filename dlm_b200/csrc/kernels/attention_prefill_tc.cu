@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], s_full[2], s_free[2], p_ready[2], pv_done[2];
+    __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], s_full[2], p_ready[2], pv_done[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
     __shared__ int s_map[2];
@@ -143,7 +143,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
             mbar_init(&s_full[s], 1);
-            mbar_init(&s_free[s], SOFTMAX_WARPS * 32);
             mbar_init(&p_ready[s], SOFTMAX_WARPS * 32);
             mbar_init(&pv_done[s], 1);
         }
@@ -248,8 +247,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (j + 1 < n_tiles) {
                     const int s = (j + 1) & 1;
                     if (!mbar_wait(&k_full[s], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-                    // the softmax of tile j - 1 has read this score buffer
-                    if (j + 1 >= 2 && !mbar_wait(&s_free[s], (((j + 1) >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    // (the softmax of tile j - 1 has read this score buffer: it had its scores in registers before
+                    // it announced P of tile j - 1, which this thread waited for before that tile's P V)
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(j + 1);
                 }
@@ -295,9 +294,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c = 0; c < 4; ++c) tmem_ld32_issue(s_tmem + (uint32_t)(c * 32), v[c]);
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_fence(v[c]);
-            // the scores are in registers: the buffer may take the scores of the tile after the next
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&s_free[j & 1]);
+            // the scores are in registers: once P of this tile is announced, the buffer may be written again
             // does every row of this warp see every key of the tile?  Then nothing is masked.
             const bool row_all = j0 + BKV - 1 <= pos && (p.window <= 0 || pos - j0 < p.window);
             const bool warp_all = __all_sync(0xffffffffu, row_all);
