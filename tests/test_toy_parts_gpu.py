@@ -1,6 +1,7 @@
 """Parts defined outside the package can be registered, built and stepped without a change
-to the package's files: a mixer that keeps state of its own per request, and a whole toy
-architecture around it with its own config class.  The toy is not a model of anyone's."""
+to the package's files: a mixer that keeps state of its own per request, a feed-forward with routing
+of its own, two position encodings, and whole toy architectures around them with their own config
+classes.  The toys are not models of anyone's."""
 from dataclasses import dataclass
 
 import pytest
@@ -139,3 +140,155 @@ def test_toy_mixer_with_state(tmp_path):
     assert outs == [eng.generate(reqs["t1"], max_new_tokens=5), eng.generate(reqs["t3"], max_new_tokens=5)]
     for p, o in zip((reqs["t1"], reqs["t3"]), outs):
         assert int(torch.argmax(plain_toy(folder, p)[-1])) == o[0]
+
+
+def define_routed_toy():
+    """A feed-forward with routing of its own, a rotary encoding with its own table, and an encoding that acts
+    on the embedded tokens: all defined here, none of them in the package."""
+    from dlm_b200.parts.base import FeedForward, ParamSpec, PartSpec, PositionEncoding
+    from dlm_b200.parts.model import ModelSpec
+    from dlm_b200.registry import register_architecture, register_part
+
+    class ToyHardTop1Experts(FeedForward):
+        """Each token goes to the one expert with the largest router logit, with weight 1 (no softmax):
+        the routing is the toy's, the permutation and the grouped products are the package's kernels."""
+
+        def __init__(self, hidden_size, num_experts, expert_size):
+            self.hidden, self.E, self.I = hidden_size, num_experts, expert_size
+
+        def param_specs(self):
+            return [ParamSpec("router", (self.E, self.hidden)),
+                    ParamSpec("gate_up", (self.E, 2 * self.I, self.hidden)),     # rows 2p: gate, 2p + 1: up
+                    ParamSpec("down", (self.E, self.hidden, self.I))]
+
+        def load(self, tensors, rt):
+            self.router, self.gate_up, self.down = (rt.matrix(tensors[n]).contiguous() for n in ("router", "gate_up", "down"))
+
+        def forward(self, h, resid, ctx, pre_norm=None):
+            ops = ctx.rt.ops
+            logits = ops.linear(h, self.router, None, torch.float32)
+            ids = torch.argmax(logits, dim=-1, keepdim=True).to(torch.int32)
+            wts = torch.ones_like(ids, dtype=torch.float32)
+            offsets, rows, dest = ops.moe_permute(ids, self.E)
+            act = ops.grouped_swiglu(h, self.gate_up, offsets, rows)
+            ops.moe_combine(ops.grouped_linear(act, self.down, offsets), dest, wts, None, None, resid)
+
+    class ToySlowHalfRotary(PositionEncoding):
+        """Rotates only the first half of each head, at half the usual frequencies."""
+
+        def __init__(self, head_dim, base):
+            self.rd = head_dim // 2
+            self.table = torch.tensor([0.5 * base ** (-2.0 * i / self.rd) for i in range(self.rd // 2)],
+                                      dtype=torch.float64).to(torch.float32)
+
+        def rotary(self, rt):
+            return self.table.to(rt.device), self.rd
+
+    class ToySinusoidOnEmbedding(PositionEncoding):
+        """Adds scale * sin(position * 10^(-i / H)) to feature i of the embedded token."""
+
+        def __init__(self, hidden_size, scale):
+            self.freqs = torch.tensor([10.0 ** (-i / hidden_size) for i in range(hidden_size)], dtype=torch.float32)
+            self.scale = scale
+
+        def on_embed(self, x, positions, rt):
+            x += self.scale * torch.sin(positions.to(torch.float32)[:, None] * self.freqs.to(x.device)[None, :])
+
+    @dataclass
+    class RoutedToyConfig:
+        hidden_size: int
+        vocab_size: int
+        num_hidden_layers: int
+        num_experts: int
+        expert_size: int
+        rms_norm_eps: float = 1e-6
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+        def to_dict(self):
+            d = dict(self.__dict__)
+            d["architectures"] = ["ToyRoutedLM"]
+            return d
+
+    def build_spec(cfg):
+        norm = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps})
+        mixer = PartSpec("gqa_attention", {"hidden_size": cfg.hidden_size, "num_heads": 3, "num_kv_heads": 1,
+                                           "head_dim": 16, "qkv_bias": False, "window": None,
+                                           "position": PartSpec("toy_slow_half_rotary", {"head_dim": 16, "base": 500.0})})
+        ffn = PartSpec("toy_hard_top1", {"hidden_size": cfg.hidden_size, "num_experts": cfg.num_experts,
+                                         "expert_size": cfg.expert_size})
+        n = cfg.num_hidden_layers
+        return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size,
+                         layers=[PartSpec("prenorm", {"norm1": norm, "mixer": mixer, "norm2": norm, "ffn": ffn})] * n,
+                         layer_prefixes=[f"toy.layers.{i}." for i in range(n)], final_norm=norm,
+                         final_norm_prefix="toy.norm.", embed_name="toy.embed.weight", lm_head_name="toy.head.weight",
+                         embed_position=PartSpec("toy_sinusoid_on_embedding", {"hidden_size": cfg.hidden_size, "scale": 0.05}))
+
+    register_part("ffn", "toy_hard_top1", ToyHardTop1Experts)
+    register_part("position", "toy_slow_half_rotary", ToySlowHalfRotary)
+    register_part("position", "toy_sinusoid_on_embedding", ToySinusoidOnEmbedding)
+    register_architecture("ToyRoutedLM", RoutedToyConfig, build_spec)
+    return RoutedToyConfig
+
+
+def plain_routed_toy(folder, tokens):
+    """The routed toy over a whole sequence in plain PyTorch (double precision); also the gap between the two
+    largest router logits at every position (the smallest over the layers)."""
+    import plain_qwen2_moe as plain
+    cfg, t = plain.load_folder(folder)
+    t = {k: v.double() for k, v in t.items()}
+    T, H = len(tokens), cfg["hidden_size"]
+    pos = torch.arange(T)
+    x = t["toy.embed.weight"][torch.tensor(tokens)]
+    freqs = torch.tensor([10.0 ** (-i / H) for i in range(H)], dtype=torch.float32)
+    x = x + (0.05 * torch.sin(pos.to(torch.float32)[:, None] * freqs[None, :])).double()
+    inv = torch.tensor([0.5 * 500.0 ** (-2.0 * i / 8) for i in range(4)], dtype=torch.float64).to(torch.float32)
+    gap = torch.full((T,), float("inf"), dtype=torch.float64)
+
+    def half_rope(v):                                  # [T, heads, 16]: the first 8 dims rotate
+        return torch.cat([plain.rope(v[..., :8], pos, inv), v[..., 8:]], dim=-1)
+
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"toy.layers.{i}."
+        n = plain.rmsnorm(x, t[p + "norm1.weight"], cfg["rms_norm_eps"])
+        q, k, v = (n @ t[p + f"mixer.{c}_proj.weight"].T for c in "qkv")
+        ctx = plain.attention(half_rope(q.view(T, 3, 16)), half_rope(k.view(T, 1, 16)), v.view(T, 1, 16), None)
+        x = x + ctx.reshape(T, 48) @ t[p + "mixer.o_proj.weight"].T
+        n2 = plain.rmsnorm(x, t[p + "norm2.weight"], cfg["rms_norm_eps"])
+        logits = n2 @ t[p + "ffn.router"].T
+        top2 = torch.topk(logits, 2, dim=-1).values
+        gap = torch.minimum(gap, top2[:, 0] - top2[:, 1])
+        choice = torch.argmax(logits, dim=-1)
+        out = torch.zeros_like(x)
+        for j in range(T):
+            w_gu, w_d = t[p + "ffn.gate_up"][choice[j]], t[p + "ffn.down"][choice[j]]
+            out[j] = plain.swiglu_ffn(n2[j:j + 1], w_gu[0::2], w_gu[1::2], w_d, lambda z: z)[0]
+        x = x + out
+    return plain.rmsnorm(x, t["toy.norm.weight"], cfg["rms_norm_eps"]) @ t["toy.head.weight"].T, gap
+
+
+def test_toy_routing_and_position_encodings(tmp_path):
+    import cuttings
+    from dlm_b200.engine import Engine
+    from dlm_b200.weights import write_random_model
+    RoutedToyConfig = define_routed_toy()
+    cfg = RoutedToyConfig(hidden_size=40, vocab_size=113, num_hidden_layers=3, num_experts=5, expert_size=24)
+    folder = write_random_model(cfg, 11, str(tmp_path / "routed"))
+    eng = Engine.from_pretrained(folder, dtype="float32", page_size=16, num_pages=24, max_requests=4)
+    g = torch.Generator().manual_seed(5)
+    reqs = {f"t{i}": torch.randint(0, 113, (n,), generator=g).tolist() for i, n in enumerate([37, 8, 66, 21])}
+    ref = {rid: plain_routed_toy(folder, toks) for rid, toks in reqs.items()}
+    mixed, _ = cuttings.mixed(reqs, max_live=3, seed=6)
+    compared = 0
+    for steps in (cuttings.whole(reqs), cuttings.portions(reqs), cuttings.tail_decode(reqs, 10), mixed):
+        got = cuttings.run_trace(eng, steps)
+        assert len(got) == sum(map(len, reqs.values()))
+        for (rid, p), row in got.items():
+            logits, gap = ref[rid]
+            if float(gap[p]) < 1e-5:          # a tie of the hard routing within rounding: either expert is right
+                continue
+            assert float((row.double() - logits[p]).abs().max()) < 1e-4, (rid, p)
+            compared += 1
+    assert compared > 0.9 * 4 * sum(map(len, reqs.values()))
