@@ -130,7 +130,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window) -> torc
     nkv = k.shape[1]
     group = nh // nkv
     scale = 1.0 / math.sqrt(hd)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     allowed = pos[None, :] <= pos[:, None]
     if window is not None:
         allowed &= (pos[:, None] - pos[None, :]) < window
@@ -191,7 +191,7 @@ def moe_ffn(x, lw, cfg: PlainConfig, rnd, x_router=None):
         if lw.get("shared_gate") is not None:
             gate = 1.0 / (1.0 + torch.exp(-(xr @ lw["shared_gate"].T)))    # [T, 1]
         else:
-            gate = torch.ones(x.shape[0], 1, dtype=x.dtype)
+            gate = torch.ones(x.shape[0], 1, dtype=x.dtype, device=x.device)
         out = out + gate * sh
     return out
 
@@ -224,20 +224,23 @@ def decoder_layer(x, lw, cfg: PlainConfig, layer_index: int, positions, inv_freq
 
 # ------------------------------------------------------------------------- model
 class PlainModel:
-    def __init__(self, path: str, compute=torch.float64, emulate_bf16: bool = False):
-        raw, tensors = load_folder(path)
+    def __init__(self, path, compute=torch.float64, emulate_bf16: bool = False, device="cpu"):
+        """``path``: a model folder, or a pair (config dict, tensors by name).  ``device``: where the
+        plain computation runs (the GPU is only a faster place for the same PyTorch statements)."""
+        raw, tensors = path if isinstance(path, tuple) else load_folder(path)
+        self.device = torch.device(device)
         self.cfg = cfg = PlainConfig(raw)
         self.compute = compute
         self.rnd = bf16_round if emulate_bf16 else (lambda t: t)
 
         def mat(name):      # a matrix: rounded to bfloat16 first when that path is emulated
-            t = tensors[name].to(torch.float32)
+            t = tensors[name].to(self.device).to(torch.float32)
             if emulate_bf16:
                 t = t.to(torch.bfloat16).to(torch.float32)
             return t.to(compute)
 
         def vec(name):      # norm weights and biases keep what they were stored with
-            return tensors[name].to(torch.float32).to(compute)
+            return tensors[name].to(self.device).to(torch.float32).to(compute)
 
         self.embed = mat("model.embed_tokens.weight")
         self.final_norm = vec("model.norm.weight")
@@ -267,7 +270,7 @@ class PlainModel:
             else:                                           # src/loader.rs:395-399
                 lw["dense"] = tuple(mat(f"{p}mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
             self.layers.append(lw)
-        self.inv_freq = rope_inv_freqs(cfg.hd, cfg.theta)
+        self.inv_freq = rope_inv_freqs(cfg.hd, cfg.theta).to(self.device)
 
     def hidden_states(self, tokens, layer_order=None) -> torch.Tensor:
         """Residual stream after the last layer for the whole sequence [T, H]."""
@@ -275,8 +278,9 @@ class PlainModel:
         ids = torch.as_tensor(tokens, dtype=torch.long)
         if ids.numel() == 0 or int(ids.max()) >= cfg.V or int(ids.min()) < 0:
             raise ValueError("empty prompt or token outside the vocabulary")   # src/generate.rs:315-325
+        ids = ids.to(self.device)
         x = self.embed[ids]                                  # row copy, no scaling
-        positions = torch.arange(ids.numel())
+        positions = torch.arange(ids.numel(), device=self.device)
         order = range(cfg.L) if layer_order is None else layer_order
         for i in order:
             x = decoder_layer(x, self.layers[i], cfg, i, positions, self.inv_freq, self.rnd)
@@ -296,14 +300,14 @@ class PlainModel:
             MARGIN_LOG = None
         if not gaps:
             return torch.full((len(tokens),), float("inf"), dtype=torch.float64)
-        return torch.stack([g.to(torch.float64) for g in gaps]).min(dim=0).values
+        return torch.stack([g.to(torch.float64) for g in gaps]).min(dim=0).values.cpu()
 
     def logits(self, tokens, layer_order=None) -> torch.Tensor:
         """src/generate.rs:328-331 at every position: rmsnorm with model.norm, then the head.
         Returns [T, V] as 32-bit floats."""
         x = self.hidden_states(tokens, layer_order)
         n = self.rnd(rmsnorm(x, self.final_norm, self.cfg.eps))
-        return (n @ self.lm_head.T).to(torch.float32)
+        return (n @ self.lm_head.T).to(torch.float32).cpu()
 
 
 # ---------------------------------------------------------------------- sampling
