@@ -276,6 +276,10 @@ ATT_CASES = [
     (3, 1, 128, 128, 0, [(513, 513), (129, 128)]),
     (2, 1, 256, 16, 0, [(50, 50), (33, 1)]),
     (4, 4, 80, 16, 40, [(130, 130)]),
+    # single tokens only: lengths around a tile's and a page's edge, more heads in a group than a tile has rows
+    (20, 1, 64, 128, 0, [(1, 1), (63, 1), (64, 1), (65, 1), (1500, 1), (128, 1), (129, 1)]),
+    (4, 2, 128, 256, 200, [(700, 1), (199, 1), (200, 1), (201, 1), (5000, 1), (257, 1)]),
+    (6, 3, 64, 64, 0, [(4097, 1), (17, 1)]),
 ]
 
 
