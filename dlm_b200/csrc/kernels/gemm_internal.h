@@ -42,4 +42,11 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
              const float* bias, void* out, int ldo, int M, int N, int K, int out_dtype, int epilogue,
              cudaStream_t stream);
 
+// The same on pairs of multiprocessors (tcgen05.mma.cta_group::2: 256 weight rows a tile); gemm_tc tries it
+// first when N > 128.  Off with DLM_B200_NO_PAIR=1.
+bool gemm_tc_pair_enabled();
+bool gemm_tc_pair(const void* a, int lda, const void* w, int ldw, const int32_t* expert_offsets, int num_experts,
+                  const float* bias, void* out, int ldo, int M, int N, int K, int out_dtype, int epilogue,
+                  cudaStream_t stream);
+
 }  // namespace dlmk

@@ -33,6 +33,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "gemm_internal.h"
+#include "gemm_tc_common.cuh"
 #include "tcgen05.cuh"
 
 namespace dlmk {
@@ -44,53 +45,8 @@ using namespace tc5;
 constexpr int BM = 128, BK = 64;
 constexpr int EPI_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, THREADS = 320;
 
-struct TcParams {
-    const int32_t* expert_offsets; int num_experts;
-    const float* bias;
-    void* out; int ldo;
-    int M, N, K;
-    int* err;
-};
-
-constexpr int TT = 256;          // most tokens per tile (the MMA's N)
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-struct TileInfo { int expert, row_begin, row_end; };
-
-// Token tile `ty` of the launch: dense, rows [ty * TT, ...); grouped, the ty-th tile when every expert's rows
-// are cut into tiles of TT.  expert < 0: there is no such tile.
-__device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty) {
-    TileInfo t{0, ty * TT, p.M};
-    if (p.expert_offsets != nullptr) {
-        t.expert = -1;
-        int acc = 0;
-        for (int e = 0; e < p.num_experts; ++e) {
-            const int r0 = p.expert_offsets[e], r1 = p.expert_offsets[e + 1];
-            const int tiles_e = (r1 - r0 + TT - 1) / TT;
-            if (ty < acc + tiles_e) {
-                t.expert = e;
-                t.row_begin = r0 + (ty - acc) * TT;
-                t.row_end = r1;
-                break;
-            }
-            acc += tiles_e;
-        }
-    }
-    t.row_end = min(min(t.row_end, t.row_begin + TT), p.M);
-    if (t.row_begin >= t.row_end) t.expert = -1;
-    return t;
-}
-
 // Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulators in tensor memory
 // alternate, so that the epilogue of one tile runs while the MMAs of the next are issued.
-// Token tiles are fetched with the smallest of sixteen boxes (16, 32, ..., 256 rows) that holds the tile's tokens,
-// so that a short group does not cost the bandwidth of a full one.
-struct TokenMaps { CUtensorMap m[16]; };
-
 template <int STAGES, int G, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_a, TcParams p, int nx,
@@ -233,123 +189,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!mbar_wait(&acc_full[b], u & 1, abort_flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (int t = 0; t < n_w; ++t) {
-            const int n0 = n_first + t * BM;
-            const uint32_t d_tmem = tmem_base + (b + t) * TT + ((uint32_t)(q * 32) << 16);
-            const int colw = n0 + q * 32;                        // first output column of this warp
-            const int col = colw + lane;
-            const bool col_ok = col < p.N;
-            const float bias = (EPI == EPI_STORE && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
-#pragma unroll 1
-            for (int c0 = hsel * 32; c0 < n_mma; c0 += 64) {
-                uint32_t v[32];
-                tmem_ld32(d_tmem + (uint32_t)c0, v);
-                const int tok0 = row_begin + c0;
-                const int n_valid = min(32, row_end - tok0);      // tokens of this chunk that exist
-                if (n_valid <= 0) continue;                       // uniform over the warp
-                if (EPI == EPI_SWIGLU) {
-                    // even lanes hold gate, their odd neighbours up: the even lane of a pair takes the even
-                    // tokens, the odd lane the odd ones.  The result is rounded to bfloat16: the fast
-                    // exponential and division are exact enough.
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float mine = __uint_as_float(v[j]);
-                        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                        if ((j & 1) == (lane & 1)) {
-                            const float g = (lane & 1) ? other : mine, uu = (lane & 1) ? mine : other;
-                            st[j * 17 + (lane >> 1)] = __fdividef(g, 1.0f + __expf(-g)) * uu;
-                        }
-                    }
-                    __syncwarp();
-                    TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + (colw >> 1);
-                    if (vec_ok && sizeof(TOut) == 2) {
-                        // 32 tokens x 16 outputs: a lane stores 8 outputs (16 bytes) of one token, two passes
-#pragma unroll
-                        for (int pass = 0; pass < 2; ++pass) {
-                            const int j = pass * 16 + (lane >> 1), seg = (lane & 1) * 8;
-                            if (j < n_valid && colw + 2 * seg + 15 < p.N) {
-                                const float* r = st + j * 17 + seg;
-                                uint4 pk;
-                                pk.x = pack2(r[0], r[1]); pk.y = pack2(r[2], r[3]);
-                                pk.z = pack2(r[4], r[5]); pk.w = pack2(r[6], r[7]);
-                                *reinterpret_cast<uint4*>(o + (long long)j * p.ldo + seg) = pk;
-                            }
-                        }
-                    } else {
-                        for (int idx = lane; idx < 32 * 16; idx += 32) {
-                            const int j = idx >> 4, c = idx & 15;
-                            if (j < n_valid && colw + 2 * c + 1 < p.N) o[(long long)j * p.ldo + c] = from_f32<TOut>(st[j * 17 + c]);
-                        }
-                    }
-                    __syncwarp();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) st[j * 33 + lane] = __uint_as_float(v[j]) + bias;
-                    __syncwarp();
-                    if (EPI == EPI_ADD) {
-                        float* o = static_cast<float*>(p.out) + (long long)tok0 * p.ldo + colw;
-                        if (vec_ok) {
-                            // 32 tokens x 32 columns: a lane owns 4 columns (16 bytes) of one token, eight passes;
-                            // all eight loads of the residual are in flight before the first store
-                            const int seg = (lane & 7) * 4;
-                            const bool cok = colw + seg + 3 < p.N;
-                            float4 old[8];
-#pragma unroll
-                            for (int pass = 0; pass < 8; ++pass) {
-                                const int j = pass * 4 + (lane >> 3);
-                                old[pass] = (cok && j < n_valid)
-                                                ? *reinterpret_cast<const float4*>(o + (long long)j * p.ldo + seg)
-                                                : make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-#pragma unroll
-                            for (int pass = 0; pass < 8; ++pass) {
-                                const int j = pass * 4 + (lane >> 3);
-                                if (cok && j < n_valid) {
-                                    const float* r = st + j * 33 + seg;
-                                    float4 nv = old[pass];
-                                    nv.x += r[0]; nv.y += r[1]; nv.z += r[2]; nv.w += r[3];
-                                    *reinterpret_cast<float4*>(o + (long long)j * p.ldo + seg) = nv;
-                                }
-                            }
-                        } else {
-                            for (int j = 0; j < n_valid; ++j)
-                                if (col_ok) o[(long long)j * p.ldo + lane] += st[j * 33 + lane];
-                        }
-                    } else {
-                        TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + colw;
-                        if (vec_ok && sizeof(TOut) == 4) {
-                            const int seg = (lane & 7) * 4;
-                            const bool cok = colw + seg + 3 < p.N;
-#pragma unroll
-                            for (int pass = 0; pass < 8; ++pass) {
-                                const int j = pass * 4 + (lane >> 3);
-                                if (cok && j < n_valid) {
-                                    const float* r = st + j * 33 + seg;
-                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + (long long)j * p.ldo + seg) =
-                                        make_float4(r[0], r[1], r[2], r[3]);
-                                }
-                            }
-                        } else if (vec_ok && sizeof(TOut) == 2) {
-                            const int seg = (lane & 3) * 8;
-                            const bool cok = colw + seg + 7 < p.N;
-#pragma unroll
-                            for (int pass = 0; pass < 4; ++pass) {
-                                const int j = pass * 8 + (lane >> 2);
-                                if (cok && j < n_valid) {
-                                    const float* r = st + j * 33 + seg;
-                                    uint4 pk;
-                                    pk.x = pack2(r[0], r[1]); pk.y = pack2(r[2], r[3]);
-                                    pk.z = pack2(r[4], r[5]); pk.w = pack2(r[6], r[7]);
-                                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(o) + (long long)j * p.ldo + seg) = pk;
-                                }
-                            }
-                        } else {
-                            for (int j = 0; j < n_valid; ++j)
-                                if (col_ok) o[(long long)j * p.ldo + lane] = from_f32<TOut>(st[j * 33 + lane]);
-                        }
-                    }
-                    __syncwarp();
-                }
-            }
+                const uint32_t d_tmem = tmem_base + (b + t) * TT + ((uint32_t)(q * 32) << 16);
+                const int colw = n_first + t * BM + q * 32;       // first output column of this warp
+                epilogue_tile<EPI, TOut>(p, st, d_tmem, colw, n_mma, row_begin, row_end, hsel, lane, vec_ok);
             }
             // this accumulator may be written again
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -374,21 +216,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ----------------------------------------------------------------------------- host side
-// rows x K bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64 elements, 128-byte swizzle,
-// elements outside the matrix read as zero
-bool make_map(CUtensorMap* map, const void* base, long long rows, int K, int ld, int box_rows,
-              CUtensorMapL2promotion promote = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
-    EncodeTiledFn fn = encode_tiled();
-    if (fn == nullptr) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promote,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 int sm_count() {
     static int n = 0;
     if (n == 0) {
@@ -436,6 +263,9 @@ bool gemm_tc(const void* a, int lda, const void* w, int ldw, const int32_t* expe
     DLM_CHECK(epilogue != EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N");
     DLM_CHECK(epilogue != EPI_ADD || out_dtype == F32, "gemm: the accumulate epilogue needs a float32 output");
     DLM_CHECK(bias == nullptr || epilogue == EPI_STORE, "gemm: a bias goes with the store epilogue only");
+    if (N > BM && gemm_tc_pair_enabled() &&
+        gemm_tc_pair(a, lda, w, ldw, expert_offsets, num_experts, bias, out, ldo, M, N, K, out_dtype, epilogue, stream))
+        return true;
     CUtensorMap mw;
     TokenMaps ma;
     const long long w_rows = expert_offsets ? (long long)num_experts * N : N;

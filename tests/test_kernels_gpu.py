@@ -82,7 +82,7 @@ def test_rmsnorm_hand_value(ops):
 # ------------------------------------------------------------------------ products
 GEMM_SHAPES = [(1, 64, 64), (5, 97, 130), (64, 128, 256), (130, 200, 72), (257, 330, 1000), (3, 1408, 2048),
                (8, 2048, 1408), (16, 100, 72), (33, 200, 200), (2, 48, 40), (9, 2816, 2048), (1, 300, 5632),
-               (65, 128, 64), (300, 264, 40), (513, 2816, 2048), (1000, 96, 1408)]
+               (65, 128, 64), (300, 264, 40), (513, 2816, 2048), (1000, 96, 1408), (100, 384, 192)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
