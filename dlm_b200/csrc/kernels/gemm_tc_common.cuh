@@ -29,26 +29,26 @@ constexpr int TT = 256;          // most tokens per tile (the MMA's N)
 
 struct TileInfo { int expert, row_begin, row_end; };
 
-// Token tile `ty` of the launch: dense, rows [ty * TT, ...); grouped, the ty-th tile when every expert's rows
-// are cut into tiles of TT.  expert < 0: there is no such tile.
-__device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty) {
-    TileInfo t{0, ty * TT, p.M};
+// Token tile `ty` of the launch: dense, rows [ty * tt, ...); grouped, the ty-th tile when every expert's rows
+// are cut into tiles of tt (at most TT) tokens.  expert < 0: there is no such tile.
+__device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty, int tt = TT) {
+    TileInfo t{0, ty * tt, p.M};
     if (p.expert_offsets != nullptr) {
         t.expert = -1;
         int acc = 0;
         for (int e = 0; e < p.num_experts; ++e) {
             const int r0 = p.expert_offsets[e], r1 = p.expert_offsets[e + 1];
-            const int tiles_e = (r1 - r0 + TT - 1) / TT;
+            const int tiles_e = (r1 - r0 + tt - 1) / tt;
             if (ty < acc + tiles_e) {
                 t.expert = e;
-                t.row_begin = r0 + (ty - acc) * TT;
+                t.row_begin = r0 + (ty - acc) * tt;
                 t.row_end = r1;
                 break;
             }
             acc += tiles_e;
         }
     }
-    t.row_end = min(min(t.row_end, t.row_begin + TT), p.M);
+    t.row_end = min(min(t.row_end, t.row_begin + tt), p.M);
     if (t.row_begin >= t.row_end) t.expert = -1;
     return t;
 }
@@ -58,21 +58,21 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& p, int ty) {
 // bandwidth of a full one.
 struct TokenMaps { CUtensorMap m[16]; };
 
-// Warp `hsel` (0 or 1) of a quadrant takes the chunks of 32 tokens c0 = 32 hsel, 32 hsel + 64, ...  `d_tmem`
-// addresses the accumulator's first column in this warp's 32 lanes, `colw` is the warp's first output column,
-// `st` its staging area of 32 x 33 floats.
-template <int EPI, typename TOut>
+// Warp `hsel` (0 or 1) of a quadrant takes the chunks of CH tokens c0 = CH hsel, CH hsel + 2 CH, ...  (CH = 32,
+// or 16 where the staging areas have to be small).  `d_tmem` addresses the accumulator's first column in
+// this warp's 32 lanes, `colw` is the warp's first output column, `st` its staging area of CH x 33 floats.
+template <int EPI, typename TOut, int CH = 32>
 __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint32_t d_tmem, int colw, int n_mma,
                                               int row_begin, int row_end, int hsel, int lane, bool vec_ok) {
     const int col = colw + lane;
     const bool col_ok = col < p.N;
     const float bias = (EPI == EPI_STORE && p.bias != nullptr && col_ok) ? p.bias[col] : 0.f;
 #pragma unroll 1
-    for (int c0 = hsel * 32; c0 < n_mma; c0 += 64) {
-        uint32_t v[32];
-        tmem_ld32(d_tmem + (uint32_t)c0, v);
+    for (int c0 = hsel * CH; c0 < n_mma; c0 += 2 * CH) {
+        uint32_t v[CH];
+        tmem_ld(d_tmem + (uint32_t)c0, v);
         const int tok0 = row_begin + c0;
-        const int n_valid = min(32, row_end - tok0);      // tokens of this chunk that exist
+        const int n_valid = min(CH, row_end - tok0);      // tokens of this chunk that exist
         if (n_valid <= 0) continue;                       // uniform over the warp
         if (EPI == EPI_SWIGLU) {
             // Even lanes hold gate, their odd neighbours up, for the same output.  Per pair of tokens (j, j + 1)
@@ -82,7 +82,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
             // and division are exact enough.
             const bool odd = lane & 1;
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
+            for (int j = 0; j < CH; j += 2) {
                 const float a0 = __uint_as_float(v[j]), a1 = __uint_as_float(v[j + 1]);
                 const float got = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
                 const float g = odd ? got : a0, uu = odd ? a1 : got;
@@ -91,9 +91,9 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
             __syncwarp();
             TOut* o = static_cast<TOut*>(p.out) + (long long)tok0 * p.ldo + (colw >> 1);
             if (vec_ok && sizeof(TOut) == 2) {
-                // 32 tokens x 16 outputs: a lane stores 8 outputs (16 bytes) of one token, two passes
+                // CH tokens x 16 outputs: a lane stores 8 outputs (16 bytes) of one token, 16 tokens a pass
 #pragma unroll
-                for (int pass = 0; pass < 2; ++pass) {
+                for (int pass = 0; pass < CH / 16; ++pass) {
                     const int j = pass * 16 + (lane >> 1), seg = (lane & 1) * 8;
                     if (j < n_valid && colw + 2 * seg + 15 < p.N) {
                         const float* r = st + j * 17 + seg;
@@ -104,7 +104,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
                     }
                 }
             } else {
-                for (int idx = lane; idx < 32 * 16; idx += 32) {
+                for (int idx = lane; idx < CH * 16; idx += 32) {
                     const int j = idx >> 4, c = idx & 15;
                     if (j < n_valid && colw + 2 * c + 1 < p.N) o[(long long)j * p.ldo + c] = from_f32<TOut>(st[j * 17 + c]);
                 }
@@ -112,25 +112,25 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
             __syncwarp();
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) st[j * 33 + lane] = __uint_as_float(v[j]) + bias;
+            for (int j = 0; j < CH; ++j) st[j * 33 + lane] = __uint_as_float(v[j]) + bias;
             __syncwarp();
             if (EPI == EPI_ADD) {
                 float* o = static_cast<float*>(p.out) + (long long)tok0 * p.ldo + colw;
                 if (vec_ok) {
-                    // 32 tokens x 32 columns: a lane owns 4 columns (16 bytes) of one token, eight passes;
-                    // all eight loads of the residual are in flight before the first store
+                    // CH tokens x 32 columns: a lane owns 4 columns (16 bytes) of one token, 4 tokens a pass;
+                    // all loads of the residual are in flight before the first store
                     const int seg = (lane & 7) * 4;
                     const bool cok = colw + seg + 3 < p.N;
-                    float4 old[8];
+                    float4 old[CH / 4];
 #pragma unroll
-                    for (int pass = 0; pass < 8; ++pass) {
+                    for (int pass = 0; pass < CH / 4; ++pass) {
                         const int j = pass * 4 + (lane >> 3);
                         old[pass] = (cok && j < n_valid)
                                         ? *reinterpret_cast<const float4*>(o + (long long)j * p.ldo + seg)
                                         : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
 #pragma unroll
-                    for (int pass = 0; pass < 8; ++pass) {
+                    for (int pass = 0; pass < CH / 4; ++pass) {
                         const int j = pass * 4 + (lane >> 3);
                         if (cok && j < n_valid) {
                             const float* r = st + j * 33 + seg;
@@ -149,7 +149,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
                     const int seg = (lane & 7) * 4;
                     const bool cok = colw + seg + 3 < p.N;
 #pragma unroll
-                    for (int pass = 0; pass < 8; ++pass) {
+                    for (int pass = 0; pass < CH / 4; ++pass) {
                         const int j = pass * 4 + (lane >> 3);
                         if (cok && j < n_valid) {
                             const float* r = st + j * 33 + seg;
@@ -161,7 +161,7 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, float* st, uint
                     const int seg = (lane & 3) * 8;
                     const bool cok = colw + seg + 7 < p.N;
 #pragma unroll
-                    for (int pass = 0; pass < 4; ++pass) {
+                    for (int pass = 0; pass < CH / 8; ++pass) {
                         const int j = pass * 8 + (lane >> 2);
                         if (cok && j < n_valid) {
                             const float* r = st + j * 33 + seg;

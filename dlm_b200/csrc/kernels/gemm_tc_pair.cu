@@ -36,8 +36,7 @@ using namespace tc5;
 
 constexpr int BM = 128, BK = 64;
 constexpr int EPI_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, THREADS = 320;
-constexpr uint32_t W_BYTES = BM * BK * 2, A_HALF_BYTES = (TT / 2) * BK * 2, STAGE_BYTES = W_BYTES + A_HALF_BYTES;
-constexpr int STAGES = 5;
+constexpr uint32_t W_BYTES = BM * BK * 2;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -83,10 +82,15 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(both) : "memory");
 }
 
-template <int EPI, typename TOut>
+// STAGES stages of 128 weight rows and A_ROWS token rows (half of the tile's most tokens, `tt`); CH: tokens per
+// pass of the epilogue.  What bounds the kernel is the bytes in flight: a stage comes back to the producer only
+// some 4,000 clocks after its copy was issued (copy, wait for the tensor pipe, MMAs, commit), so the ring holds
+// all the shared memory there is, and the epilogue's staging areas are small.
+template <int STAGES, int A_ROWS, int CH, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ TokenMaps maps_a, TcParams p, int nx,
-                    int total_tiles) {
+                    int total_tiles, int tt) {
+    constexpr uint32_t STAGE_BYTES = W_BYTES + A_ROWS * BK * 2;
     // M = 256 over the pair, bfloat16 x bfloat16 -> float32, both operands K-major; N is filled in per tile
     constexpr uint32_t IDESC0 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((2 * BM) >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
@@ -113,7 +117,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     for (int i = tid; i < TABLE; i += THREADS) {
         const long long tile = (long long)pair + (long long)i * n_pairs;
-        if (tile < total_tiles) s_tiles[i] = tile_info(p, (int)(tile / nx));
+        if (tile < total_tiles) s_tiles[i] = tile_info(p, (int)(tile / nx), tt);
     }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
@@ -129,7 +133,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int k_tiles = (p.K + BK - 1) / BK;
     auto info_of = [&](int tile) -> TileInfo {
         const int i = (tile - pair) / n_pairs;
-        return i < TABLE ? s_tiles[i] : tile_info(p, tile / nx);
+        return i < TABLE ? s_tiles[i] : tile_info(p, tile / nx, tt);
     };
     dep_wait();
     dep_launch_next();
@@ -204,7 +208,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else {
         const int q = warp & 3, hsel = warp >> 2;
-        float* st = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES) + warp * (32 * 33);
+        float* st = reinterpret_cast<float*>(tiles + (size_t)STAGES * STAGE_BYTES) + warp * (CH * 33);
         const bool vec_ok = (p.ldo % 8 == 0) && (p.N % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
         const uint32_t leader_empty0 = cluster_addr(&acc_empty[0], 0);
         uint32_t acc_i = 0;
@@ -223,7 +227,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (n0 < p.N) {
                 const uint32_t d_tmem = tmem_base + b * TT + ((uint32_t)(q * 32) << 16);
-                epilogue_tile<EPI, TOut>(p, st, d_tmem, n0 + q * 32, n_mma, ti.row_begin, ti.row_end, hsel, lane, vec_ok);
+                epilogue_tile<EPI, TOut, CH>(p, st, d_tmem, n0 + q * 32, n_mma, ti.row_begin, ti.row_end, hsel, lane, vec_ok);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -275,13 +279,16 @@ int sm_count_pair() {
     return n;
 }
 
-template <int EPI, typename TOut>
-void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int nx, int total_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 32 * 33 * sizeof(float) + 1024;
-    auto kern = gemm_tc_pair_kernel<EPI, TOut>;
+template <int STAGES, int A_ROWS, int EPI, typename TOut>
+void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int nx, int total_tiles, int tt,
+            cudaStream_t stream) {
+    constexpr int CH = 16;
+    constexpr size_t smem = (size_t)STAGES * (W_BYTES + A_ROWS * BK * 2) + EPI_WARPS * CH * 33 * sizeof(float) + 1024;
+    static_assert(smem + 1024 <= 227 * 1024, "the ring does not fit in shared memory");
+    auto kern = gemm_tc_pair_kernel<STAGES, A_ROWS, CH, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int pairs = total_tiles < sm_count_pair() / 2 ? total_tiles : sm_count_pair() / 2;
-    launch_pair(kern, 2 * pairs, smem, stream, mw, ma, p, nx, total_tiles);
+    launch_pair(kern, 2 * pairs, smem, stream, mw, ma, p, nx, total_tiles, tt);
 }
 
 }  // namespace
@@ -306,19 +313,26 @@ bool gemm_tc_pair(const void* a, int lda, const void* w, int ldw, const int32_t*
     for (int i = 0; i < 16; ++i)
         if (!make_map(&ma.m[i], a, M, K, lda, 8 * (i + 1))) return false;
     TcParams p{expert_offsets, num_experts, bias, out, ldo, M, N, K, error_flag_ptr()};
-    int t_tiles = (M + TT - 1) / TT;
-    if (expert_offsets != nullptr) t_tiles += num_experts;
+    // Grouped: tiles of at most 160 tokens, so that a stage is 26 KB and eight of them fit (an expert with more
+    // tokens takes several tiles); dense: 256 tokens a tile, six stages of 32 KB.
+    const bool grouped = expert_offsets != nullptr;
+    const int tt = grouped ? 160 : TT;
+    int t_tiles = (M + tt - 1) / tt;
+    if (grouped) t_tiles += num_experts;
     const int nx = (N + 2 * BM - 1) / (2 * BM);
     DLM_CHECK((long long)nx * t_tiles < (1LL << 30), "gemm: too many tiles for one launch");
     const int total_tiles = nx * t_tiles;
     const bool f32 = out_dtype == F32;
-    switch (epilogue) {
-        case EPI_STORE: if (f32) launch<EPI_STORE, float>(mw, ma, p, nx, total_tiles, stream);
-                        else launch<EPI_STORE, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;
-        case EPI_ADD: launch<EPI_ADD, float>(mw, ma, p, nx, total_tiles, stream); break;
-        default: if (f32) launch<EPI_SWIGLU, float>(mw, ma, p, nx, total_tiles, stream);
-                 else launch<EPI_SWIGLU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, stream); break;
+#define DLM_PAIR(ST, AR)                                                                                          \
+    switch (epilogue) {                                                                                           \
+        case EPI_STORE: if (f32) launch<ST, AR, EPI_STORE, float>(mw, ma, p, nx, total_tiles, tt, stream);        \
+                        else launch<ST, AR, EPI_STORE, __nv_bfloat16>(mw, ma, p, nx, total_tiles, tt, stream); break; \
+        case EPI_ADD: launch<ST, AR, EPI_ADD, float>(mw, ma, p, nx, total_tiles, tt, stream); break;              \
+        default: if (f32) launch<ST, AR, EPI_SWIGLU, float>(mw, ma, p, nx, total_tiles, tt, stream);              \
+                 else launch<ST, AR, EPI_SWIGLU, __nv_bfloat16>(mw, ma, p, nx, total_tiles, tt, stream); break;   \
     }
+    if (grouped) { DLM_PAIR(8, 80) } else { DLM_PAIR(6, 128) }
+#undef DLM_PAIR
     check_launch("gemm_tc_pair");
     return true;
 }
