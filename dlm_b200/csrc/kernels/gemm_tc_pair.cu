@@ -297,7 +297,11 @@ bool gemm_tc_pair_enabled() {
     static int state = -1;
     if (state < 0) {
         const char* off = std::getenv("DLM_B200_NO_PAIR");
-        state = (off != nullptr && off[0] != '\0' && off[0] != '0') ? 0 : 1;
+        int dev = 0, clusters = 0;
+        cudaGetDevice(&dev);
+        const bool can = cudaDeviceGetAttribute(&clusters, cudaDevAttrClusterLaunch, dev) == cudaSuccess && clusters != 0 &&
+                         sm_count_pair() >= 2;
+        state = (off != nullptr && off[0] != '\0' && off[0] != '0') || !can ? 0 : 1;
     }
     return state == 1;
 }

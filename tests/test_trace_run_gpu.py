@@ -110,3 +110,30 @@ def test_overlapped_launches_change_no_bit(dtype, tiny_folders, tmp_path):
     assert outs[0].keys() == outs[1].keys() and outs[0]
     for key in outs[0]:
         assert torch.equal(outs[0][key], outs[1][key]), f"{key} differs"
+
+
+@pytest.mark.parametrize("switch", ["DLM_B200_NO_PAIR", "DLM_B200_NO_TCGEN05", "DLM_B200_NO_STREAM"])
+def test_older_kernels_give_the_same_answers(switch, tiny_folders, tmp_path):
+    """Each switch that takes an older kernel (single-SM tcgen05 products, warp-level MMA and cp.async instead
+    of tcgen05 and TMA, per-lane loads instead of bulk copies) leaves the logits within the bfloat16 tolerance
+    of the plain implementation: a fault in a fallback does not wait for the day it is needed."""
+    name, dtype = "D", "bfloat16"       # head_dim 128: the tcgen05 attention and the TMA decode attention are in play
+    V = TINY[name]["cfg"]["vocab_size"]
+    oracle = plain.PlainModel(tiny_folders[name], compute=torch.float64, emulate_bf16=True)
+    toks = {f"q{i}": prompt(400 + i, n, V) for i, n in enumerate([150, 40, 97, 20])}
+    margins = {rid: oracle.router_margins(t) for rid, t in toks.items()}
+    steps, _ = cuttings.mixed(toks, max_live=4, seed=13)
+    peak = cuttings.peak_tokens(steps)
+    out_dir = str(tmp_path / "out")
+    replay(tiny_folders[name], dtype, steps, out_dir, peak, env={switch: "1"})
+    got = read_logits(out_dir, steps, V)
+    assert got, "no logits were written"
+    full = {rid: oracle.logits(t) for rid, t in toks.items()}
+    checked = 0
+    for (rid, p), row in got.items():
+        if float(margins[rid][p]) < MARGIN[dtype]:
+            continue
+        d = float((row - full[rid][p]).abs().max())
+        assert d <= TOL[dtype], f"{switch}: {rid} position {p}: {d:.3e}"
+        checked += 1
+    assert checked > 0.5 * len(got)
