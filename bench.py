@@ -2,6 +2,7 @@
 random weights (bfloat16) on one B200, plus prefill, roofline and end-to-end figures.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload serving      # continuous batching on the windowed model, a line of its own
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -120,6 +121,66 @@ def run_reference():
     return 0
 
 
+def run_serving(args) -> int:
+    """Continuous batching on the windowed variant of the model: 64 requests, prompt lengths uniform in
+    [256, 16384], output lengths uniform in [64, 512], seeded uniform token ids; a request arrives every
+    second step, so portions of prompts (2,048-token portions) run beside decoded tokens in the same step.
+    Everything goes through the scheduler and the Python entry point; one JSON line."""
+    import torch
+
+    from dlm_b200.config import Qwen2MoeConfig
+    from dlm_b200.engine import Engine
+
+    raw = dict(MODEL)
+    raw.update(num_hidden_layers=args.layers, use_sliding_window=True, sliding_window=4096,
+               max_window_layers=min(21, max(args.layers - 3, 0)), max_position_embeddings=32768)
+    cfg = Qwen2MoeConfig.from_dict(raw)
+    torch.cuda.set_device(0)
+    n_req, pool_tokens, max_context = 64, 262144, 16384 + 512 + 64
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=pool_tokens,
+                             max_requests=n_req, max_step_tokens=2048, max_context=max_context)
+    gen = torch.Generator().manual_seed(4)
+    plen = torch.randint(256, 16385, (n_req,), generator=gen).tolist()
+    olen = torch.randint(64, 513, (n_req,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in plen]
+    # warm-up: one short request end to end (kernels loaded, graphs of its shapes captured)
+    eng.generate([prompts[0][:300]], max_new_tokens=4)
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    submitted, produced, steps = 0, 0, 0
+    while submitted < n_req or eng.scheduler.has_work():
+        if submitted < n_req and steps % 2 == 0:
+            eng.submit(prompts[submitted], max_new_tokens=olen[submitted])
+            submitted += 1
+        out = eng.run_step()
+        produced += len(out)
+        steps += 1
+    torch.cuda.synchronize()
+    t1 = time.time()
+    time.sleep(0.2)
+    sampler.stop()
+    clocks = sampler.summary(t0, t1)
+    st = eng.stats()
+    ok = st["finished"] >= n_req and produced == sum(olen)
+    line = {
+        "metric": "serving: generated tok/s, 64 requests, prompts 256-16384, outputs 64-512, continuous batching "
+                  "(Qwen1.5-MoE-A2.7B sizes, layers 21-23 windowed at 4096, bf16, random weights)",
+        "value": round(produced / (t1 - t0), 2), "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)", "impl": "ours",
+        "seconds": round(t1 - t0, 3), "generated_tokens": produced, "prompt_tokens": sum(plen),
+        "prompt_tok_s": round(sum(plen) / (t1 - t0), 1), "steps": steps, "complete": ok,
+        "config": {"model": "Qwen1.5-MoE-A2.7B sizes, window", "requests": n_req, "layers": args.layers,
+                   "layers_full": FULL_LAYERS, "pool_tokens": pool_tokens, "portion": 2048, "page_size": 64,
+                   "arrivals": "one request every second step"},
+        "scheduler": {k: st[k] for k in ("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished")},
+        "pages": st["pages"], "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0 if ok else 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -132,12 +193,16 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="serving: the continuous-batching workload on the windowed model, instead of the default line")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload == "serving":
+        return run_serving(args)
     args.warmup = max(args.warmup, 3)
 
     import torch

@@ -155,7 +155,10 @@ Plan Scheduler::plan() {
         const int pending = (int)r.tokens.size() - r.computed;
         const int slot = cache_->open();
         const int reserve = (int)running_.size();
-        const int n = cache_->max_appendable(slot, std::min(pending, budget), reserve);
+        int n = cache_->max_appendable(slot, std::min(pending, budget), reserve);
+        // Beside running requests a prompt is admitted only if all of it fits in what is free now: a prompt
+        // that gets its first portion and then has to give its pages back is computed twice.
+        if (n > 0 && !running_.empty() && cache_->max_appendable(slot, pending, reserve) < pending) n = 0;
         if (n == 0) {
             cache_->close(slot);
             if (running_.empty() && plan.items.empty()) {   // an empty engine cannot hold one token of it

@@ -176,6 +176,27 @@ def test_preemption_when_pages_run_out(host):
     assert seen_restart
 
 
+def test_a_prompt_waits_until_all_of_it_fits(host):
+    """Beside a running request a prompt is admitted only when the free pages hold all of it (it would get a
+    first portion and lose it again otherwise); alone it is admitted whatever its length."""
+    # pool of 10 pages of 16 tokens; request 0: prompt of 64 tokens (4 pages), decodes 40 more (up to 7 pages);
+    # request 1: prompt of 100 tokens = 7 pages, which do not fit beside request 0's 4 + 1 spare
+    cache, sched = make(host, pages=10, budget=32, rows=4)
+    trace = []
+    res = drive(cache, sched, [[3] * 64, [5] * 100], 40, trace=trace)
+    assert res[0] == (alone([3] * 64, 40), "length") and res[1] == (alone([5] * 100, 40), "length")
+    assert sched.stats().preemptions == 0
+    first_of_1 = next(i for i, plan in enumerate(trace) if any(it.id == 1 for it in plan.items))
+    last_of_0 = max(i for i, plan in enumerate(trace) if any(it.id == 0 for it in plan.items))
+    assert first_of_1 > last_of_0                    # request 1 started only when request 0 had left
+    # a prompt that does fit whole is admitted beside the running request, portion by portion
+    cache2, sched2 = make(host, pages=16, budget=32, rows=4)
+    trace2 = []
+    res2 = drive(cache2, sched2, [[3] * 64, [5] * 100], 40, trace=trace2)
+    assert res2[0] == (alone([3] * 64, 40), "length") and res2[1] == (alone([5] * 100, 40), "length")
+    assert any(len({it.id for it in plan.items}) == 2 for plan in trace2)
+
+
 def test_request_that_can_never_fit_fails_alone(host):
     cache, sched = make(host, pages=2, budget=64)
     res = drive(cache, sched, [[1] * 20, [2] * 10], 30)
