@@ -164,10 +164,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
     } else if (warp == MMA_WARP) {
-        // The whole warp walks the loop and one elected lane issues: addresses and descriptors are then the
-        // same in every lane, which the compiler keeps in the warp's uniform registers, where tcgen05.mma
-        // takes its operands from (computed by a single lane of a divergent branch, each descriptor has to be
-        // moved there first, and the issuing lane, not the tensor pipe, sets the pace).  The next slice's
+        // The whole warp walks the loop and one elected lane issues, so that addresses and descriptors are the
+        // same in every lane (a loop of "wait, four MMAs, commit" walked by one lane of a divergent branch cost
+        // that lane 540 clocks an iteration in a probe kernel, walked by the warp 390).  The next slice's
         // barrier is asked before the MMAs of this one are issued, and the answer read after them.
         if (rank == 0) {
             uint32_t it = 0, acc_i = 0;
