@@ -8,25 +8,22 @@ namespace {
 
 constexpr int ROUTER_THREADS = 256;
 
-// 8 consecutive elements of a row as floats (one 16-byte load for bfloat16, two for float32).
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+// 4 consecutive elements of a row as floats (one 8-byte load for bfloat16, one 16-byte load for float32).
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+    v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+    v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
 }
-__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
 }
 
 // Router logits: blockIdx.x = token, blockIdx.y = a block of ROUTER_WARPS experts, one warp per
 // expert.  Each logit is one warp's dot product summed in a fixed order (lane l takes elements
-// 8l..8l+7 of every 256, then a shuffle tree), so routing does not depend on what else is in the
-// batch.  VEC: rows are 16-byte aligned and H is a multiple of 8.
+// 4l..4l+3 and 128+4l..128+4l+3 of every 256, so that a quarter warp reads 128 consecutive bytes of the
+// staged row and no two lanes meet in a bank; then a shuffle tree), so routing does not depend on what
+// else is in the batch.  VEC: rows are 16-byte aligned and H is a multiple of 8.
 // With norm_w != nullptr the input is the 32-bit residual and the RMS norm (weight norm_w, eps)
 // is applied here, in 32-bit, so that the router never sees a rounded activation.
 constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
@@ -59,13 +56,17 @@ router_logits_kernel(const TX* h, const T* __restrict__ w, const float* __restri
     float s = 0.f;
     if (VEC) {
 #pragma unroll 4
-        for (int i = lane * 8; i < H; i += 256) {
-            float wv[8];
-            load8(wr + i, wv);
-            const float4 xa = *reinterpret_cast<const float4*>(x + i), xb = *reinterpret_cast<const float4*>(x + i + 4);
-            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        for (int b = 0; b < H; b += 256) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) s = fmaf(xv[j], wv[j], s);
+            for (int half = 0; half < 2; ++half) {
+                const int i = b + 128 * half + lane * 4;
+                if (i < H) {
+                    float wv[4];
+                    load4(wr + i, wv);
+                    const float4 xa = *reinterpret_cast<const float4*>(x + i);
+                    s = fmaf(xa.x, wv[0], s); s = fmaf(xa.y, wv[1], s); s = fmaf(xa.z, wv[2], s); s = fmaf(xa.w, wv[3], s);
+                }
+            }
         }
     } else {
         for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
@@ -134,22 +135,27 @@ router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __
         for (int a = 0; a < ROUTER_EW; ++a)
 #pragma unroll
             for (int j = 0; j < ROUTER_TB; ++j) s[a][j] = 0.f;
-        for (int i = lane * 8; i < H; i += 256) {
-            float wv[ROUTER_EW][8];
+        for (int b = 0; b < H; b += 256) {
 #pragma unroll
-            for (int a = 0; a < ROUTER_EW; ++a) {
-                const int e = min(e0 + a, rows - 1);            // rows beyond the table repeat the last one (not stored)
-                load8(w + (long long)e * H + i, wv[a]);
-            }
+            for (int half = 0; half < 2; ++half) {
+                const int i = b + 128 * half + lane * 4;       // the elements of router_logits_kernel's lane
+                if (i < H) {
+                    float wv[ROUTER_EW][4];
 #pragma unroll
-            for (int j = 0; j < ROUTER_TB; ++j) {
-                const float* x = smem + (size_t)j * H + i;
-                const float4 xa = *reinterpret_cast<const float4*>(x), xb = *reinterpret_cast<const float4*>(x + 4);
-                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                    for (int a = 0; a < ROUTER_EW; ++a) {
+                        const int e = min(e0 + a, rows - 1);    // rows beyond the table repeat the last one (not stored)
+                        load4(w + (long long)e * H + i, wv[a]);
+                    }
 #pragma unroll
-                for (int a = 0; a < ROUTER_EW; ++a)
+                    for (int j = 0; j < ROUTER_TB; ++j) {
+                        const float4 xa = *reinterpret_cast<const float4*>(smem + (size_t)j * H + i);
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) s[a][j] = fmaf(xv[q], wv[a][q], s[a][j]);
+                        for (int a = 0; a < ROUTER_EW; ++a) {
+                            s[a][j] = fmaf(xa.x, wv[a][0], s[a][j]); s[a][j] = fmaf(xa.y, wv[a][1], s[a][j]);
+                            s[a][j] = fmaf(xa.z, wv[a][2], s[a][j]); s[a][j] = fmaf(xa.w, wv[a][3], s[a][j]);
+                        }
+                    }
+                }
             }
         }
 #pragma unroll
