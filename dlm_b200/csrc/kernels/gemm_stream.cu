@@ -28,10 +28,13 @@
 #include "api.h"
 #include "common.cuh"
 #include "gemm_internal.h"
+#include "tcgen05.cuh"
 
 namespace dlmk {
 
 namespace {
+
+using namespace tc5;      // mbarrier helpers with bounded waits
 
 constexpr int CW = 8;                        // consumer warps
 constexpr int THREADS = (CW + 1) * 32;       // + the producer warp
@@ -39,7 +42,6 @@ constexpr int RT = 16;                       // rows of W per tile
 constexpr int STAGES = 3;
 constexpr int KC_MAX = 2048;                 // most elements of a row per stage
 constexpr int MAX_ACTIVE = 1024;             // most experts with rows in one launch
-constexpr uint32_t WAIT_LIMIT = 1u << 22;    // try_wait calls before a wait gives up
 
 struct StreamParams {
     const __nv_bfloat16* a; int lda; const int32_t* a_rows;
@@ -55,36 +57,6 @@ struct StreamParams {
     int* err;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return done != 0;
-}
-// Bounded wait.  Returns false when it gave up (or another role already had): the caller stops.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
 // One row piece: global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned.
 __device__ __forceinline__ void bulk_copy(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
