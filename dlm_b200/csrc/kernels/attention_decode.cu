@@ -7,6 +7,7 @@
 #include "api.h"
 #include "attention_internal.h"
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace dlmk {
 
@@ -34,10 +35,6 @@ template <> struct Vec8<float> {
     }
 };
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");

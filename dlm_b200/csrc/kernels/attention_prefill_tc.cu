@@ -25,6 +25,7 @@
 #include "api.h"
 #include "attention_internal.h"
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "tcgen05.cuh"
 
 namespace dlmk {
@@ -53,10 +54,6 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(

@@ -9,6 +9,7 @@
 // it lies in.
 #include "api.h"
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "gemm_internal.h"
 
 namespace dlmk {
@@ -36,12 +37,6 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_s
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_src));
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-                 "{%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 template <int BM, int EPI, typename TOut>

@@ -19,6 +19,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "gemm_internal.h"
 
 namespace dlmk {
@@ -51,13 +52,6 @@ __device__ __forceinline__ void prefetch_l2(const void* p) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-                 "{%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 template <int NT, int EPI, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32) gemm_smallm_kernel(SmallParams p) {
