@@ -548,12 +548,7 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
         // This kernel is fastest with one block per multiprocessor and as few key splits as that allows (a
         // block's start and the merge of splits cost more than a second wave saves); never more splits than
         // the plan, whose scratch it uses.
-        static const int n_sm = []() {
-            int dev = 0, n = 0;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-            return n > 0 ? n : 148;
-        }();
+        const int n_sm = sm_count();
         const long long per_split = (long long)R * nkv * head_passes;
         int splits = (int)(n_sm / per_split);
         splits = splits < 1 ? 1 : (splits > n_splits ? n_splits : splits);

@@ -267,16 +267,6 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
 }
 
-int sm_count_attn() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
-
 template <int HD>
 void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache,
             const int32_t* block_table, int table_width, const int32_t* cu_q, const int32_t* kv_len, void* out, int R,
@@ -290,7 +280,7 @@ void launch(dim3 grid, cudaStream_t stream, const void* q, const void* k_cache, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
         static_cast<const __nv_bfloat16*>(v_cache), block_table, table_width, cu_q, kv_len,
         static_cast<__nv_bfloat16*>(out), R, nh, nkv, page_size, total_pages, shift, window,
-        scale * 1.4426950408889634f, skip_single, sm_count_attn(), error_flag_ptr());
+        scale * 1.4426950408889634f, skip_single, sm_count(), error_flag_ptr());
 }
 
 }  // namespace

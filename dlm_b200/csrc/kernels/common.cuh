@@ -88,6 +88,9 @@ inline void launch_dep(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem,
     cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);   // an error shows in check_launch()
 }
 
+// Multiprocessors of the current device (asked once).
+int sm_count();
+
 // Device pointer of the host-mapped error flag (see take_error_flag in api.h).
 int* error_flag_ptr();
 

@@ -37,6 +37,16 @@ bool dep_launch_enabled() {
 }
 void set_dep_launch(bool on) { g_dep_launch = on ? 1 : 0; }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 int take_error_flag() {
     if (g_flag_host == nullptr) return 0;
     int v = *reinterpret_cast<volatile int*>(g_flag_host);
@@ -315,7 +325,7 @@ __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
     dep_launch_next();
     const int t = blockIdx.x;
     float* r = resid + (long long)t * H;
-    if (VEC) {
+    if constexpr (VEC) {
         // four columns a thread; per element the same sums in the same order as below
         const float g = (shared != nullptr && gate != nullptr) ? gate[t] : 1.0f;
         for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H / 4; i += blockDim.x * gridDim.y) {
@@ -335,17 +345,17 @@ __global__ void moe_combine_kernel(const float* y, const int32_t* dest,
             cur.x += acc.x; cur.y += acc.y; cur.z += acc.z; cur.w += acc.w;
             *reinterpret_cast<float4*>(r + 4 * i) = cur;
         }
-        return;
-    }
-    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += blockDim.x * gridDim.y) {
-        float acc = 0.f;
-        for (int j = 0; j < k; ++j)
-            acc = fmaf(wts[t * k + j], y[(long long)dest[t * k + j] * H + i], acc);
-        if (shared != nullptr) {
-            const float g = gate ? gate[t] : 1.0f;
-            acc = fmaf(g, shared[(long long)t * H + i], acc);
+    } else {
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += blockDim.x * gridDim.y) {
+            float acc = 0.f;
+            for (int j = 0; j < k; ++j)
+                acc = fmaf(wts[t * k + j], y[(long long)dest[t * k + j] * H + i], acc);
+            if (shared != nullptr) {
+                const float g = gate ? gate[t] : 1.0f;
+                acc = fmaf(g, shared[(long long)t * H + i], acc);
+            }
+            r[i] += acc;
         }
-        r[i] += acc;
     }
 }
 

@@ -292,16 +292,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
     if (tid == 0 && s_abort) *p.err = 5;
 }
 
-int sm_count_stream() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
-
 template <int NT, int EPI, typename TOut>
 void launch_one(const StreamParams& p, int grid, cudaStream_t stream) {
     const size_t smem = (size_t)STAGES * RT * p.pitch + 2 * sizeof(float) * CW * 16 * (8 * NT + 1);
@@ -369,7 +359,7 @@ void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, i
     p.err = error_flag_ptr();
     const int groups = expert_offsets ? (num_experts < M ? num_experts : M) : 1;
     const long long items = (long long)p.tiles * groups;
-    const int grid = (int)(items < sm_count_stream() ? items : sm_count_stream());
+    const int grid = (int)(items < sm_count() ? items : sm_count());
     if (nt == 1) launch_nt<1>(p, grid, out_dtype, epilogue, stream);
     else if (nt == 2) launch_nt<2>(p, grid, out_dtype, epilogue, stream);
     else launch_nt<4>(p, grid, out_dtype, epilogue, stream);

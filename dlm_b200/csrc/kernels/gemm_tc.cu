@@ -216,16 +216,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ----------------------------------------------------------------------------- host side
-int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 132;
-    }
-    return n;
-}
-
 template <int G, int EPI, typename TOut>
 void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int nx, int total_tiles,
             cudaStream_t stream) {

@@ -268,16 +268,6 @@ void launch_pair(void (*kernel)(P...), int grid, size_t smem, cudaStream_t strea
     cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);   // an error shows in check_launch()
 }
 
-int sm_count_pair() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 132;
-    }
-    return n;
-}
-
 template <int STAGES, int A_ROWS, int EPI, typename TOut>
 void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int nx, int total_tiles, int tt,
             cudaStream_t stream) {
@@ -286,7 +276,7 @@ void launch(const CUtensorMap& mw, const TokenMaps& ma, const TcParams& p, int n
     static_assert(smem + 1024 <= 227 * 1024, "the ring does not fit in shared memory");
     auto kern = gemm_tc_pair_kernel<STAGES, A_ROWS, CH, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    const int pairs = total_tiles < sm_count_pair() / 2 ? total_tiles : sm_count_pair() / 2;
+    const int pairs = total_tiles < sm_count() / 2 ? total_tiles : sm_count() / 2;
     launch_pair(kern, 2 * pairs, smem, stream, mw, ma, p, nx, total_tiles, tt);
 }
 
@@ -299,7 +289,7 @@ bool gemm_tc_pair_enabled() {
         int dev = 0, clusters = 0;
         cudaGetDevice(&dev);
         const bool can = cudaDeviceGetAttribute(&clusters, cudaDevAttrClusterLaunch, dev) == cudaSuccess && clusters != 0 &&
-                         sm_count_pair() >= 2;
+                         sm_count() >= 2;
         state = (off != nullptr && off[0] != '\0' && off[0] != '0') || !can ? 0 : 1;
     }
     return state == 1;
