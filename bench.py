@@ -29,6 +29,11 @@ MODEL = dict(
     norm_topk_prob=False, decoder_sparse_step=1, intermediate_size=5632, vocab_size=151936, rope_theta=1000000.0,
     rms_norm_eps=1e-6, use_sliding_window=False, tie_word_embeddings=False, max_position_embeddings=4096)
 FULL_LAYERS = MODEL["num_hidden_layers"]
+MODEL_NAME = "Qwen1.5-MoE-A2.7B"
+# The larger model of the same family (--sizes 57b; about 114 GB of weights with all 28 layers).
+SIZES_57B = dict(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                 num_experts=64, num_experts_per_tok=8, moe_intermediate_size=2560,
+                 shared_expert_intermediate_size=20480, intermediate_size=20480)
 
 
 def peaks():
@@ -190,12 +195,20 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (reported)")
+    ap.add_argument("--sizes", default="a2.7b", choices=["a2.7b", "57b"],
+                    help="57b: the layer sizes of Qwen2-57B-A14B instead (not the default line)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
                     help="serving: the continuous-batching workload on the windowed model, instead of the default line")
     args = ap.parse_args()
+    global FULL_LAYERS, MODEL_NAME
+    if args.sizes == "57b":
+        MODEL.update(SIZES_57B)
+        FULL_LAYERS, MODEL_NAME = SIZES_57B["num_hidden_layers"], "Qwen2-57B-A14B"
+    if args.layers is None:
+        args.layers = FULL_LAYERS
     if args.impl == "reference":
         return run_reference()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -302,13 +315,13 @@ def main() -> int:
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
     out = {
-        "metric": "decode tok/s @ batch 8 (Qwen1.5-MoE-A2.7B sizes, bf16, random weights)",
+        "metric": "decode tok/s @ batch %d (%s sizes, bf16, random weights)" % (args.batch, MODEL_NAME),
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
         "impl": "ours",
         "config": {
-            "model": "Qwen1.5-MoE-A2.7B sizes", "global_batch": args.batch, "seq_len": args.context,
+            "model": MODEL_NAME + " sizes", "global_batch": args.batch, "seq_len": args.context,
             "parallelism": "1 GPU", "prompt_len": args.prompt_len, "layers": args.layers, "layers_full": FULL_LAYERS,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
