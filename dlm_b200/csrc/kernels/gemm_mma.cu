@@ -33,11 +33,6 @@ __device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gme
     const int bytes = valid ? 16 : 0;      // 0 source bytes: the 16 destination bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_src) {
-    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_src));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
 
 template <int BM, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS) gemm_mma_kernel(MmaParams p) {
@@ -142,11 +137,11 @@ __global__ void __launch_bounds__(THREADS) gemm_mma_kernel(MmaParams p) {
         for (int kk = 0; kk < BK; kk += 16) {
             uint32_t af[MT][4], bf[2][4];
 #pragma unroll
-            for (int i = 0; i < MT; ++i) ldmatrix_x4(af[i], at + (i * 16 + lm_row) * PITCH + kk + lm_col);
+            for (int i = 0; i < MT; ++i) ldsm_x4(af[i], at + (i * 16 + lm_row) * PITCH + kk + lm_col);
             // W rows are the product's columns: a 16 (n) x 16 (k) tile gives the B fragments of two n8 tiles:
             // registers {0, 2} = (n 0-7, k 0-7 | k 8-15), {1, 3} = (n 8-15, k 0-7 | k 8-15)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) ldmatrix_x4(bf[j], bt + (j * 16 + lm_row) * PITCH + kk + lm_col);
+            for (int j = 0; j < 2; ++j) ldsm_x4(bf[j], bt + (j * 16 + lm_row) * PITCH + kk + lm_col);
 #pragma unroll
             for (int i = 0; i < MT; ++i)
 #pragma unroll
