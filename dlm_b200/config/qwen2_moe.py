@@ -3,9 +3,16 @@
 Every size and constant of the model comes from ``config.json`` through this
 class; nothing downstream carries a literal size.  Keys, defaults and refusals
 follow the reference's parser (src/model/config.rs:42-94, 235-274, 425-501);
-the five keys it does not read (``use_sliding_window``, ``sliding_window``,
-``max_window_layers``, ``decoder_sparse_step``, ``mlp_only_layers``) and
-``tie_word_embeddings`` are defined here.
+the keys it does not read (``use_sliding_window``, ``sliding_window``,
+``max_window_layers``, ``layer_types``, ``decoder_sparse_step``,
+``mlp_only_layers``) and ``tie_word_embeddings`` are defined here.
+
+Which layers are windowed: an explicit ``layer_types`` list (one of
+``"full_attention"`` / ``"sliding_attention"`` per layer) wins when the key is
+present; otherwise layer ``i`` is windowed iff ``use_sliding_window`` and
+``i >= max_window_layers``.  (Other software that writes this key may derive
+another default from ``max_window_layers``; a folder that carries the list is
+therefore read by the list, never by the rule.)
 """
 from __future__ import annotations
 
@@ -15,6 +22,15 @@ from typing import Any
 
 from .base import (ConfigError, as_bool, as_float, as_int, eos_list,
                    read_config_json, require_int)
+
+
+LAYER_TYPES = ("full_attention", "sliding_attention")
+
+
+def _layer_types(v: Any) -> list[str]:
+    if not isinstance(v, (list, tuple)) or not all(isinstance(t, str) for t in v):
+        raise ConfigError("layer_types must be a list of strings")
+    return list(v)
 
 
 @dataclass
@@ -44,6 +60,7 @@ class Qwen2MoeConfig:
     use_sliding_window: bool = False
     sliding_window: int | None = None
     max_window_layers: int = 0
+    layer_types: list[str] | None = None   # explicit per-layer choice; None: the max_window_layers rule
 
     architecture = "Qwen2MoeForCausalLM"
     model_type = "qwen2_moe"
@@ -115,6 +132,7 @@ class Qwen2MoeConfig:
             if raw.get("sliding_window") is not None else None,
             max_window_layers=as_int(raw["max_window_layers"], "max_window_layers", minimum=0)
             if raw.get("max_window_layers") is not None else 0,
+            layer_types=_layer_types(raw["layer_types"]) if raw.get("layer_types") is not None else None,
         )
         cfg.validate()
         return cfg
@@ -150,6 +168,15 @@ class Qwen2MoeConfig:
         if self.use_sliding_window:
             if self.sliding_window is None or self.sliding_window <= 0:
                 raise ConfigError("use_sliding_window is true but sliding_window is missing or not > 0")
+        if self.layer_types is not None:
+            if len(self.layer_types) != self.num_hidden_layers:
+                raise ConfigError(f"layer_types has {len(self.layer_types)} entries, the model has "
+                                  f"{self.num_hidden_layers} layers")
+            for i, t in enumerate(self.layer_types):
+                if t not in LAYER_TYPES:
+                    raise ConfigError(f"layer_types[{i}] is {t!r}; known: {list(LAYER_TYPES)}")
+            if "sliding_attention" in self.layer_types and (self.sliding_window is None or self.sliding_window <= 0):
+                raise ConfigError("layer_types names a sliding_attention layer but sliding_window is missing or not > 0")
         for t in self.eos_token_ids:
             if t < 0:
                 raise ConfigError("eos_token_id must be >= 0")
@@ -163,8 +190,11 @@ class Qwen2MoeConfig:
                 and (i + 1) % self.decoder_sparse_step == 0)
 
     def layer_window(self, i: int) -> int | None:
-        """Layer ``i`` sees only the last ``sliding_window`` positions (itself included)
-        iff ``use_sliding_window`` and ``i >= max_window_layers``."""
+        """The window of layer ``i`` (it sees only the last ``sliding_window`` positions, itself
+        included) or None.  ``layer_types[i]`` decides when the list is given; otherwise the layer
+        is windowed iff ``use_sliding_window`` and ``i >= max_window_layers``."""
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[i] == "sliding_attention" else None
         if self.use_sliding_window and i >= self.max_window_layers:
             return self.sliding_window
         return None

@@ -2,7 +2,8 @@
 
 Per layer, from the config: attention with or without a sliding window
 (``layer_window``), and a routed mixture of experts or a dense MLP
-(``layer_is_sparse``).  Tensor names are the checkpoint's own
+(``layer_is_sparse``).  A shared expert whose gate tensor the checkpoint lacks
+is taken with the factor 1, as the reference does (src/forward/cpu.rs:1032-1041).  Tensor names are the checkpoint's own
 (src/loader.rs:392-418, 434-453): nothing is renamed.
 """
 from __future__ import annotations
@@ -28,7 +29,7 @@ def build_spec(cfg: Qwen2MoeConfig) -> ModelSpec:
             ffn = PartSpec("moe_softmax_topk", {
                 "hidden_size": cfg.hidden_size, "num_experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
                 "expert_intermediate_size": cfg.moe_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob,
-                "shared_intermediate_size": cfg.shared_expert_intermediate_size, "shared_gate": True})
+                "shared_intermediate_size": cfg.shared_expert_intermediate_size, "shared_gate": None})
         else:
             ffn = PartSpec("swiglu_dense", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size})
         layers.append(PartSpec("prenorm", {"norm1": norm, "mixer": mixer, "norm2": norm, "ffn": ffn, "names": _NAMES}))

@@ -44,19 +44,23 @@ class SoftmaxTopKMoE(FeedForward):
     logits in 32-bit from the 32-bit normalised residual, softmax over all experts, the k largest probabilities (ties: lower
     expert first), optionally renormalised; each chosen expert's SwiGLU output scaled by its
     weight and summed from zero in routing order; then an optional shared expert scaled by
-    ``sigmoid(shared_gate · h)`` (1 when ``shared_gate`` is False); the sum goes to the residual.
+    ``sigmoid(shared_gate · h)``; the sum goes to the residual.  ``shared_gate``: True, the gate
+    tensor is required; False, there is none and the factor is 1; None, the checkpoint decides:
+    a missing gate tensor means the factor 1 (src/forward/cpu.rs:1032-1041).
 
     At load the experts are stacked into ``[E, 2I, H]`` (gate and up rows interleaved) and
     ``[E, H, I]``; the router and the shared gate become one ``[E (+1), H]`` matrix."""
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_intermediate_size: int,
-                 norm_topk_prob: bool, shared_intermediate_size: int | None = None, shared_gate: bool = True):
+                 norm_topk_prob: bool, shared_intermediate_size: int | None = None,
+                 shared_gate: bool | None = True):
         self.hidden, self.E, self.k, self.I = int(hidden_size), int(num_experts), int(top_k), int(expert_intermediate_size)
         if not (1 <= self.k <= self.E):
             raise ValueError("top_k must be in 1..num_experts")
         self.norm = bool(norm_topk_prob)
         self.Is = int(shared_intermediate_size) if shared_intermediate_size else None
-        self.has_gate = bool(shared_gate) and self.Is is not None
+        self.shared_gate = shared_gate if self.Is is not None else False
+        self.has_gate = bool(self.shared_gate)      # None: settled when the tensors are loaded
         self.w_router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
 
     def param_specs(self):
@@ -69,12 +73,15 @@ class SoftmaxTopKMoE(FeedForward):
             specs += [ParamSpec("shared_expert.gate_proj.weight", (self.Is, self.hidden)),
                       ParamSpec("shared_expert.up_proj.weight", (self.Is, self.hidden)),
                       ParamSpec("shared_expert.down_proj.weight", (self.hidden, self.Is))]
-            if self.has_gate:
-                specs.append(ParamSpec("shared_expert_gate.weight", (1, self.hidden)))
+            if self.shared_gate is not False:
+                specs.append(ParamSpec("shared_expert_gate.weight", (1, self.hidden),
+                                       optional=self.shared_gate is None))
         return specs
 
     def load(self, tensors, rt: Runtime):
         rows = [rt.matrix(tensors["gate.weight"])]
+        self.has_gate = (self.shared_gate is True
+                         or (self.shared_gate is None and "shared_expert_gate.weight" in tensors))
         if self.has_gate:
             rows.append(rt.matrix(tensors["shared_expert_gate.weight"]).reshape(1, self.hidden))
         self.w_router = torch.cat(rows, dim=0).contiguous()

@@ -67,6 +67,7 @@ class PlainConfig:
         self.use_window = bool(raw.get("use_sliding_window") or False)
         self.window = raw.get("sliding_window")
         self.max_window_layers = raw.get("max_window_layers") or 0
+        self.layer_types = raw.get("layer_types")
         self.tie = bool(raw.get("tie_word_embeddings") or False)
 
     def is_sparse(self, i: int) -> bool:
@@ -75,7 +76,10 @@ class PlainConfig:
         return self.E > 0 and i not in self.mlp_only and (i + 1) % self.sparse_step == 0
 
     def layer_window(self, i: int):
-        """Layer i is windowed iff use_sliding_window and i >= max_window_layers."""
+        """An explicit layer_types list decides ("sliding_attention" = windowed); without one,
+        layer i is windowed iff use_sliding_window and i >= max_window_layers."""
+        if self.layer_types is not None:
+            return self.window if self.layer_types[i] == "sliding_attention" else None
         return self.window if (self.use_window and i >= self.max_window_layers) else None
 
 

@@ -49,6 +49,29 @@ def test_layer_rules():
     assert all(a.layer_is_sparse(i) for i in range(2)) and a.layer_window(1) is None
 
 
+def test_layer_types_win_over_the_rule():
+    raw = {**TINY["B"]["cfg"], "layer_types": ["sliding_attention", "full_attention", "sliding_attention"]}
+    c = Qwen2MoeConfig.from_dict(raw)
+    assert [c.layer_window(i) for i in range(3)] == [16, None, 16]
+    # the list decides even when use_sliding_window is false
+    c = Qwen2MoeConfig.from_dict({**raw, "use_sliding_window": False})
+    assert [c.layer_window(i) for i in range(3)] == [16, None, 16]
+    spec = registry.resolve(raw)[2]
+    assert [s.params["mixer"].params["window"] for s in spec.layers] == [16, None, 16]
+    assert Qwen2MoeConfig.from_dict(c.to_dict()) == c
+    # without the key: layer i is windowed iff use_sliding_window and i >= max_window_layers
+    c = Qwen2MoeConfig.from_dict(TINY["B"]["cfg"])
+    assert c.layer_types is None and [c.layer_window(i) for i in range(3)] == [None, 16, 16]
+    with pytest.raises(ConfigError, match="layer_types has 2"):
+        Qwen2MoeConfig.from_dict({**raw, "layer_types": ["full_attention"] * 2})
+    with pytest.raises(ConfigError, match="chunked"):
+        Qwen2MoeConfig.from_dict({**raw, "layer_types": ["chunked", "full_attention", "full_attention"]})
+    with pytest.raises(ConfigError, match="sliding_window"):
+        Qwen2MoeConfig.from_dict({**BASE, "layer_types": ["sliding_attention", "full_attention"]})
+    with pytest.raises(ConfigError, match="list of strings"):
+        Qwen2MoeConfig.from_dict({**raw, "layer_types": "sliding_attention"})
+
+
 @pytest.mark.parametrize("patch,match", [
     ({"num_attention_heads": 0}, "num_attention_heads"),
     ({"hidden_size": 66}, "divisible"),

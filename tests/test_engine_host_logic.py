@@ -143,3 +143,30 @@ def test_replay_program_protocol(tiny_folders, oracles, tmp_path, monkeypatch, c
     assert float((l0 - ra[[0, 11]]).abs().max()) < 1e-4
     assert float((l1 - rb[[8]]).abs().max()) < 1e-4
     assert float((l3 - ra[[19]]).abs().max()) < 1e-4
+
+
+def test_gateless_shared_expert_and_explicit_layer_types(tiny_folders, tmp_path):
+    """A checkpoint without the shared expert's gate tensor runs with the factor 1
+    (src/forward/cpu.rs:1032-1041), and an explicit layer_types list decides which layers are
+    windowed; both against the oracle, which reads the same folder on its own."""
+    import shutil
+    from safetensors.torch import load_file, save_file
+    V = TINY["B"]["cfg"]["vocab_size"]
+    folder = tmp_path / "variant"
+    shutil.copytree(tiny_folders["B"], folder)
+    tensors = {n: t for n, t in load_file(str(folder / "model.safetensors")).items() if "shared_expert_gate" not in n}
+    save_file(tensors, str(folder / "model.safetensors"))
+    raw = json.loads((folder / "config.json").read_text())
+    raw["layer_types"] = ["sliding_attention", "full_attention", "sliding_attention"]
+    (folder / "config.json").write_text(json.dumps(raw))
+    oracle = plain.PlainModel(str(folder), compute=torch.float64)
+    toks = prompt(3, 60, V)
+    ref = oracle.logits(toks)
+    base = plain.PlainModel(tiny_folders["B"], compute=torch.float64).logits(toks)
+    assert float((ref - base).abs().max()) > 1e-3          # the variant is another model
+    eng = engine(str(folder))
+    assert [b.mixer.window for b in eng.model.blocks] == [16, None, 16]
+    assert eng.model.blocks[1].ffn.has_gate is False
+    got = cuttings.run_trace(eng, cuttings.portions({"r": toks}))
+    for (rid, p), row in got.items():
+        assert float((row - ref[p]).abs().max()) < 1e-4

@@ -124,6 +124,22 @@ def test_bias_optional_by_presence(tmp_path, tiny_folders):
     assert model.blocks[0].mixer.b_qkv is None            # src/loader.rs:258-264
 
 
+def test_shared_gate_optional_by_presence(tmp_path, tiny_folders):
+    """A checkpoint without shared_expert_gate.weight loads; the shared expert then counts in full
+    (src/forward/cpu.rs:1032-1041)."""
+    st = TensorStore(tiny_folders["A"])
+    tensors = {n: st.tensor(n) for n in st.names() if "shared_expert_gate" not in n}
+    folder = tmp_path / "nogate"
+    folder.mkdir()
+    save_file(tensors, str(folder / "model.safetensors"))
+    (folder / "config.json").write_text(open(os.path.join(tiny_folders["A"], "config.json")).read())
+    _, model = load_model(str(folder), cpu_rt())
+    moe = model.blocks[0].ffn
+    assert moe.has_gate is False and moe.w_router.shape == (8, 64) and moe.ws_down is not None
+    _, with_gate = load_model(tiny_folders["A"], cpu_rt())
+    assert with_gate.blocks[0].ffn.has_gate is True
+
+
 def test_random_weights_are_a_function_of_seed_and_name(tmp_path):
     a = random_tensor("x.weight", (5, 7), "linear", 3)
     assert torch.equal(a, random_tensor("x.weight", (5, 7), "linear", 3))
