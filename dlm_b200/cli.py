@@ -2,6 +2,12 @@
 the same option names with the same meanings and defaults, the same output lines
 (``prompt ids   :``, ``generated ids:``).  Options the reference does not have are listed
 after its own.  There is no tokenizer: prompts are token ids.
+
+Where the model comes from, in this order: ``--model-path DIR`` (a folder with config.json and
+safetensors); ``--random CONFIG.json`` (random weights from ``--seed`` for the architecture and
+sizes that config file names, whichever registered architecture that is); else the reference's
+demo geometry options.  ``--save-random DIR`` writes the random model as a folder (config.json,
+model.safetensors) and generates from that folder.
 """
 from __future__ import annotations
 
@@ -34,6 +40,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--num-kv-heads", type=int, default=2)
     g.add_argument("--intermediate-size", type=int, default=128)
     g.add_argument("--seed", type=int, default=0, help="seed of the synthetic weights")
+    g.add_argument("--random", metavar="CONFIG.json", default=None,
+                   help="random weights for the architecture and sizes of this config.json (or of the folder "
+                        "that holds one); the geometry options are then ignored")
+    g.add_argument("--save-random", metavar="DIR", default=None,
+                   help="write the random model (config.json, model.safetensors) there and generate from it")
     g.add_argument("--device", choices=["gpu", "cpu"], default="gpu",
                    help="compute device; only gpu exists here (cpu is refused)")
     # synthetic mixture-of-experts geometry (no counterpart in the reference's demo model)
@@ -56,6 +67,18 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--max-requests", type=int, default=64)
     g.add_argument("--stats", action="store_true", help="print scheduler and cache statistics")
     return ap
+
+
+def demo_config(args) -> dict:
+    """The config.json of the demo model the geometry options describe (the reference's demo is a
+    dense model, src/main.rs:404-470; here it has experts too, since that is what this engine is for)."""
+    from .registry import architectures
+    return dict(architectures=[architectures()[0]], vocab_size=args.vocab_size, hidden_size=args.hidden_size,
+                num_hidden_layers=args.num_layers, num_attention_heads=args.num_heads,
+                num_key_value_heads=args.num_kv_heads, intermediate_size=args.intermediate_size,
+                num_experts=args.num_experts, num_experts_per_tok=args.num_experts_per_tok,
+                moe_intermediate_size=args.moe_intermediate_size,
+                shared_expert_intermediate_size=args.shared_expert_intermediate_size, norm_topk_prob=False)
 
 
 def run_generate(args) -> int:
@@ -82,23 +105,30 @@ def run_generate(args) -> int:
         eng = Engine.from_pretrained(args.model_path, **kw)
         print(f"generate     : model {args.model_path}")
     else:
-        from .config import Qwen2MoeConfig
-        cfg = Qwen2MoeConfig.from_dict(dict(
-            architectures=["Qwen2MoeForCausalLM"], vocab_size=args.vocab_size, hidden_size=args.hidden_size,
-            num_hidden_layers=args.num_layers, num_attention_heads=args.num_heads,
-            num_key_value_heads=args.num_kv_heads, intermediate_size=args.intermediate_size,
-            num_experts=args.num_experts, num_experts_per_tok=args.num_experts_per_tok,
-            moe_intermediate_size=args.moe_intermediate_size,
-            shared_expert_intermediate_size=args.shared_expert_intermediate_size, norm_topk_prob=False))
-        eng = Engine.from_random(cfg, args.seed, **kw)
-        print(f"generate     : demo with randomly-initialized weights (seed {args.seed})")
-    c = eng.config
-    print(f"model        : vocab {c.vocab_size}, hidden {c.hidden_size}, {c.num_hidden_layers} layers, "
-          f"{c.num_attention_heads} q-heads / {c.num_key_value_heads} kv-heads, head_dim {c.head_dim}")
+        from .registry import resolve
+        if args.random:
+            _, cfg, _ = resolve(args.random)
+            what = f"random weights for {args.random} (seed {args.seed})"
+        else:
+            _, cfg, _ = resolve(demo_config(args))
+            what = f"demo with randomly-initialized weights (seed {args.seed})"
+        if args.save_random:
+            from .weights import write_random_model
+            write_random_model(cfg, args.seed, args.save_random)
+            eng = Engine.from_pretrained(args.save_random, **kw)
+            what += f", written to {args.save_random}"
+        else:
+            eng = Engine.from_random(cfg, args.seed, **kw)
+        print(f"generate     : {what}")
+    c, spec = eng.config, eng.model.spec
+    line = f"model        : vocab {spec.vocab_size}, hidden {spec.hidden_size}, {len(spec.layers)} layers"
+    if all(hasattr(c, k) for k in ("num_attention_heads", "num_key_value_heads", "head_dim")):
+        line += f", {c.num_attention_heads} q-heads / {c.num_key_value_heads} kv-heads, head_dim {c.head_dim}"
+    print(line)
     for p in prompts:
-        bad = [t for t in p if t < 0 or t >= c.vocab_size]
+        bad = [t for t in p if t < 0 or t >= spec.vocab_size]
         if bad:
-            print(f"error: prompt token {max(bad)} out of vocab range {c.vocab_size}", file=sys.stderr)
+            print(f"error: prompt token {max(bad)} out of vocab range {spec.vocab_size}", file=sys.stderr)
             return 2
     print("device       : Gpu")
     outs = eng.generate(prompts, max_new_tokens=args.max_new_tokens, eos_token=args.eos_token,
