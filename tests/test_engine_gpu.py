@@ -24,6 +24,8 @@ TOL_BF16 = 1e-2
 # probability by less), 32-bit summation order by about 1e-8.
 MARGIN = {"float32": 1e-6, "bfloat16": 2e-4}
 
+FLOOR = {"float32": 0.95, "bfloat16": 0.9}
+
 LENGTHS = [1, 7, 16, 33, 70, 129]
 
 
@@ -87,8 +89,9 @@ def compare(got, oracle, reqs, dtype):
             d = float((got[(rid, p)] - ref[p]).abs().max())
             assert d <= tol, f"request {rid} (length {len(toks)}) position {p}: max abs diff {d:.3e} > {tol}"
             compared += 1
-    # the comparison must not be empty
-    floor = 0.95 if dtype == "float32" else 0.5
+    # the comparison must not be empty: the floors sit just under the smallest share seen
+    print(f"compared {compared} of {total} positions ({compared / total:.3f})")
+    floor = FLOOR[dtype]
     assert compared >= floor * total, f"only {compared} of {total} positions could be compared"
 
 

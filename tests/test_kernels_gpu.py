@@ -82,7 +82,10 @@ def test_rmsnorm_hand_value(ops):
 # ------------------------------------------------------------------------ products
 GEMM_SHAPES = [(1, 64, 64), (5, 97, 130), (64, 128, 256), (130, 200, 72), (257, 330, 1000), (3, 1408, 2048),
                (8, 2048, 1408), (16, 100, 72), (33, 200, 200), (2, 48, 40), (9, 2816, 2048), (1, 300, 5632),
-               (65, 128, 64), (300, 264, 40), (513, 2816, 2048), (1000, 96, 1408), (100, 384, 192)]
+               (65, 128, 64), (300, 264, 40), (513, 2816, 2048), (1000, 96, 1408), (100, 384, 192),
+               # the wider model's shapes: K = 3584 (q|k|v of 28 + 2 * 4 heads), the shared expert's gate/up
+               # (N = 2 * 20480) and down (K = 20480) products
+               (8, 4608, 3584), (300, 4608, 3584), (4, 40960, 3584), (200, 3584, 20480), (3, 3584, 20480)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -110,7 +113,8 @@ def test_linear_add_and_swiglu(ops, ref, dtype, M, N, K):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("E,k,T,H,I", [(5, 1, 9, 72, 40), (8, 2, 33, 64, 32), (12, 3, 130, 256, 48),
                                        (60, 4, 7, 512, 176), (12, 3, 20, 256, 48), (60, 4, 64, 2048, 1408),
-                                       (8, 2, 700, 64, 32), (60, 4, 2048, 512, 176)])
+                                       (8, 2, 700, 64, 32), (60, 4, 2048, 512, 176),
+                                       (64, 8, 8, 3584, 2560), (64, 8, 300, 3584, 2560)])
 def test_grouped_products(ops, ref, dtype, E, k, T, H, I):
     h = rand((T, H), dtype, 9)
     g = torch.Generator().manual_seed(E)
@@ -280,6 +284,9 @@ ATT_CASES = [
     (20, 1, 64, 128, 0, [(1, 1), (63, 1), (64, 1), (65, 1), (1500, 1), (128, 1), (129, 1)]),
     (4, 2, 128, 256, 200, [(700, 1), (199, 1), (200, 1), (201, 1), (5000, 1), (257, 1)]),
     (6, 3, 64, 64, 0, [(4097, 1), (17, 1)]),
+    # 7 query heads to a kv head (28 / 4), prompt portions and single tokens
+    (28, 4, 128, 64, 0, [(300, 300), (700, 1), (2500, 130)]),
+    (28, 4, 128, 64, 0, [(3000, 1), (64, 1), (1, 1)]),
 ]
 
 

@@ -18,11 +18,12 @@ def oracle_of(folder, dtype, device="cpu"):
     return plain.PlainModel(folder, compute=torch.float64, emulate_bf16=(dtype == "bfloat16"), device=device)
 
 
-def check_rows(rows, ref, margins, dtype, what, floor):
+def check_rows(rows, ref, margins, dtype, what, floor, margin=None):
     """rows: {position: logits row}.  Compares where the oracle's routing is not within rounding of a tie."""
     compared = 0
+    margin = MARGIN[dtype] if margin is None else margin
     for p, row in rows.items():
-        if float(margins[p]) < MARGIN[dtype]:
+        if float(margins[p]) < margin:
             continue
         d = float((row - ref[p]).abs().max())
         assert d <= TOL[dtype], f"{what} position {p}: max abs diff {d:.3e} > {TOL[dtype]}"
@@ -101,14 +102,27 @@ def test_long_requests_in_portions_of_2048(name, dtype, tiny_folders):
     steps[-1]["end"] = list(reqs)
     got = cuttings.run_trace(eng, steps)
     oracle = oracle_of(tiny_folders[name], dtype, device="cuda")
+    exact = oracle_of(tiny_folders[name], "float32", device="cuda")
     for rid, toks in reqs.items():
         ref, margins = oracle.logits(toks), oracle.router_margins(toks)
+        margin = None
+        if dtype == "bfloat16":
+            # Among thousands of positions some have a routing gap that bfloat16 rounding upstream closes:
+            # the rounded oracle's gaps differ from the exact oracle's by up to `turn`, so a position is
+            # compared only if its gap is twice that in both (the rule of test_real_sizes_gpu.py).
+            gap_e = exact.router_margins(toks)
+            turn = float((margins - gap_e).abs().max())
+            margins = torch.minimum(margins, gap_e)
+            margin = max(MARGIN[dtype], 2 * turn)
+            print(f"routing gaps move by up to {turn:.2e} under bfloat16 rounding")
         rows = {p: got[(rid, p)] for p in range(len(toks))}
-        check_rows(rows, ref, margins, dtype, f"tiny {name} {dtype} request {rid}", 0.6)
+        check_rows(rows, ref, margins, dtype, f"tiny {name} {dtype} request {rid}",
+                   0.99 if dtype == "float32" else 0.78, margin)
     for st in eng.cache.stats():
         assert st.used_pages == 0
     full, windowed = eng.cache.stats()
-    assert windowed.high_water < full.high_water // 2
+    # a windowed group keeps a portion's pages until the step is over: 2 x 2,048 tokens here
+    assert windowed.high_water <= 2 * (2048 // 64) + 2 < full.high_water
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
