@@ -70,7 +70,11 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     const int n_heads = min(GT, group - pass * GT);
     const int len = kv_len[r], p = len - 1;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int j_begin = max(lo, sp * chunk), j_end = min(len, (sp + 1) * chunk);
+    // the request's own visible keys [lo, len) are cut into n_splits shares (multiples of 64 keys, at most
+    // `chunk`), so that a request far shorter than the longest, or one with a window, still uses every block
+    int share = (len - lo + n_splits - 1) / n_splits;
+    share = min(chunk, (share + 63) / 64 * 64);
+    const int j_begin = min(len, lo + sp * share), j_end = min(len, lo + (sp + 1) * share);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int li = lane % LPK, ks = lane / LPK;
@@ -284,7 +288,7 @@ bool attention_decode_ok(int hd) { return hd % 8 == 0 && hd >= 16 && hd <= 256; 
 
 void attention_decode_plan(int R, int nkv, int max_kv_len, int* n_splits, int* chunk) {
     // one resident wave of blocks (three per multiprocessor), chunks of at least 64 keys
-    int splits = 444 / (R * nkv);
+    int splits = 3 * sm_count() / (R * nkv);
     const int max_splits = (max_kv_len + 63) / 64;
     splits = splits < 1 ? 1 : (splits > max_splits ? max_splits : splits);
     if (splits > 64) splits = 64;
@@ -369,6 +373,7 @@ void attention_decode_merge(const float* part_o, const float* part_ml, const int
 // ---------------------------------------------------------------------------------------------
 // The entry point that allocates nothing (see no_alloc.h for its terms).  It launches the same
 // kernels as attention_decode above; only the home of the scratch differs.
+#include <atomic>
 #include <cstdio>
 
 #include "no_alloc.h"
@@ -380,8 +385,24 @@ namespace {
 // not a device address and must never be passed to a kernel as one.
 static __device__ __align__(256) float g_noalloc_scratch[DLM_B200_NOALLOC_SCRATCH_FLOATS + 64];
 
+// The array's device address, per device.  Threads that make their first call on a device at the same
+// time each look the address up and store the same value, so a plain atomic is enough.
 constexpr int kMaxDevices = 64;
-float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::atomic<float*> g_noalloc_ptr[kMaxDevices];
+
+// Device address of the array on the current device (looked up at the first call there), or nullptr.
+float* noalloc_scratch(cudaError_t* e) {
+    int dev = -1;
+    *e = cudaGetDevice(&dev);
+    if (*e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    float* p = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        *e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+        if (*e != cudaSuccess) return nullptr;
+        g_noalloc_ptr[dev].store(p, std::memory_order_release);
+    }
+    return p;
+}
 
 void noalloc_fail(char* msg, size_t len, const char* text) {
     if (msg != nullptr && len > 0) snprintf(msg, len, "%s", text);
@@ -415,23 +436,13 @@ extern "C" int dlm_b200_decode_attention_noalloc(const void* q, const void* k_ca
         return 1;
     }
     // set-up, once per device, with that device current: the array's device address
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= kMaxDevices) {
-        noalloc_fail(err_msg, err_msg_len, "decode attention without allocation: device index out of range");
-        return 1;
+    cudaError_t e = cudaSuccess;
+    float* scratch = noalloc_scratch(&e);
+    if (scratch == nullptr) {
+        noalloc_fail(err_msg, err_msg_len, "decode attention without allocation: the built-in array's device "
+                                           "address could not be found (cudaGetSymbolAddress)");
+        return e != cudaSuccess ? (int)e : 1;
     }
-    if (g_noalloc_ptr[dev] == nullptr) {
-        float* p = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
-        if (e != cudaSuccess || p == nullptr) {
-            noalloc_fail(err_msg, err_msg_len, "decode attention without allocation: cudaGetSymbolAddress failed");
-            return e != cudaSuccess ? (int)e : 1;
-        }
-        g_noalloc_ptr[dev] = p;
-    }
-    float* scratch = g_noalloc_ptr[dev];
     int* status = reinterpret_cast<int*>(scratch + DLM_B200_NOALLOC_SCRATCH_FLOATS);
     e = cudaMemsetAsync(status, 0, sizeof(int), stream);      // the one word that must start at zero
     if (e != cudaSuccess) return (int)e;
@@ -465,4 +476,13 @@ extern "C" int dlm_b200_decode_attention_noalloc(const void* q, const void* k_ca
                                                                       hd, n_splits);
     e = cudaGetLastError();
     return (int)e;
+}
+
+extern "C" int dlm_b200_noalloc_status(int* host_status, cudaStream_t stream) {
+    if (host_status == nullptr) return 1;
+    cudaError_t e = cudaSuccess;
+    float* scratch = noalloc_scratch(&e);
+    if (scratch == nullptr) return e != cudaSuccess ? (int)e : 1;
+    return (int)cudaMemcpyAsync(host_status, scratch + DLM_B200_NOALLOC_SCRATCH_FLOATS, sizeof(int),
+                                cudaMemcpyDeviceToHost, stream);
 }

@@ -26,8 +26,20 @@
 //    status word, which each call clears on `stream` before launching.  Two calls that overlap on
 //    the GPU (different streams, or graphs replayed concurrently) race on the array: serialise them.
 //
-// Returns 0 on success; 1 for arguments the kernel cannot take (message in err_msg); a CUDA error
-// code otherwise.
+//  * A return value of 0 means "launched", not "correct".  The kernels never read through a page id
+//    that is missing (-1) or outside the pool for a key the query must see: they skip that key's page,
+//    the output is then computed without it, and they record code 3 in the status word.  A caller
+//    that cannot rule such tables out asks for the word with dlm_b200_noalloc_status after the call.
+//
+// Returns 0 once everything is launched; 1 for arguments the kernel cannot take (message in err_msg);
+// a CUDA error code otherwise.
+//
+// dlm_b200_noalloc_status: copies the status word of the calls made on this device so far (0: every
+// visible key had a page; 3: some call skipped a visible key that had no page) to `host_status` with one
+// cudaMemcpyAsync on `stream`; the value is there once the stream has reached that point (synchronise
+// the stream or an event recorded after it; use pinned memory if the copy must not block).  Each
+// attention call clears the word before it launches, so ask after each call whose answer matters.
+// Allocates nothing.  Returns 0, 1 for a null pointer, or a CUDA error code.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -55,6 +67,8 @@ __attribute__((visibility("default"))) int dlm_b200_decode_attention_noalloc(
     int max_kv_len,                // upper bound of kv_len (sizes the split)
     cudaStream_t stream,
     char* err_msg, size_t err_msg_len);
+
+__attribute__((visibility("default"))) int dlm_b200_noalloc_status(int* host_status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }
