@@ -4,9 +4,12 @@ Bookkeeping (which page belongs to whom) is native code (``csrc/host``); this
 module owns the device tensors the ids index and turns a list of
 ``(request slot, tokens, wanted places)`` into the device-side ``StepBatch``.
 
-Layout of a call's keys (values alike): ``[pages + 1, kv_heads, page_size,
-head_dim]``; a page of one kv head is a contiguous ``page_size x head_dim`` tile.
-The last page is a sink that padded rows write to; the pool never hands it out.
+A mixer declares what it caches per token as a list of tensors (keys and values
+for attention; a mixer with one latent vector per token declares one).  Layout
+of each: ``[pages + 1, heads, page_size, width]``; a page of one head is a
+contiguous ``page_size x width`` tile.  The last page is a sink that padded rows
+write to; the pool never hands it out.  Calls whose window and page size agree
+form a group with one pool of page ids and one block table per request.
 """
 from __future__ import annotations
 
@@ -32,32 +35,43 @@ class ModelCache:
         self.num_pages = int(num_pages)
         self.num_slots = int(num_slots)
         needs = model.cache_needs()
-        # groups: one per distinct window among the calls that own paged keys/values
+        # groups: one per distinct (window, page size) among the calls that own paged tensors
         self.group_windows: list[int] = []
+        self.group_page_size: list[int] = []
+        self.group_pages: list[int] = []
         self.call_group: dict[int, int] = {}
         self.call_owner: dict[int, int] = {}
-        self.k: dict[int, torch.Tensor] = {}
-        self.v: dict[int, torch.Tensor] = {}
+        self.tensors: dict[int, dict[str, torch.Tensor]] = {}
         self.state: dict[int, torch.Tensor] = {}
-        for ci, (kv, st, owner) in enumerate(needs):
+        keys: list[tuple[int, int]] = []
+        for ci, (need, st, owner) in enumerate(needs):
             self.call_owner[ci] = owner
-            if kv is not None and owner == ci:
-                w = int(kv.window or 0)
-                if w not in self.group_windows:
-                    self.group_windows.append(w)
-                self.call_group[ci] = self.group_windows.index(w)
-                shape = (self.num_pages + 1, kv.num_kv_heads, self.page_size, kv.head_dim)
-                self.k[ci] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
-                self.v[ci] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+            if need is not None and owner == ci:
+                ps = int(need.page_size or self.page_size)
+                key = (int(need.window or 0), ps)
+                if key not in keys:
+                    keys.append(key)
+                    self.group_windows.append(key[0])
+                    self.group_page_size.append(ps)
+                    # the same number of tokens in every pool
+                    self.group_pages.append(max(1, -(-self.num_pages * self.page_size // ps)))
+                g = keys.index(key)
+                self.call_group[ci] = g
+                self.tensors[ci] = {
+                    t.name: torch.zeros((self.group_pages[g] + 1, t.heads, ps, t.width), dtype=rt.dtype, device=rt.device)
+                    for t in need.tensors}
             if st is not None:
                 self.state[ci] = torch.zeros((self.num_slots, *st.shape), dtype=st.dtype, device=rt.device)
-        for ci, (kv, st, owner) in enumerate(needs):
-            if kv is not None and owner != ci:
+        for ci, (need, st, owner) in enumerate(needs):
+            if need is not None and owner != ci:
                 self.call_group[ci] = self.call_group[owner]
         if not self.group_windows:
             self.group_windows.append(0)     # a model without paged caches still counts tokens
+            self.group_page_size.append(self.page_size)
+            self.group_pages.append(self.num_pages)
         self.manager = host.CacheManager(
-            [host.GroupSpec(self.page_size, w, self.num_pages) for w in self.group_windows], self.num_slots)
+            [host.GroupSpec(ps, w, n) for ps, w, n in zip(self.group_page_size, self.group_windows, self.group_pages)],
+            self.num_slots)
         self._pinned = []
         self._ring = 0
         self.last_h2d_bytes = 0      # size of the last step's metadata copy
@@ -81,15 +95,25 @@ class ModelCache:
     def append(self, slot_and_n) -> None:
         self.manager.append(list(slot_and_n))
 
+    @property
+    def k(self) -> dict[int, torch.Tensor]:
+        """The ``k`` tensors of the calls that have one, by call."""
+        return {ci: t["k"] for ci, t in self.tensors.items() if "k" in t}
+
+    @property
+    def v(self) -> dict[int, torch.Tensor]:
+        return {ci: t["v"] for ci, t in self.tensors.items() if "v" in t}
+
     def bytes_per_token(self) -> int:
-        return sum(2 * k.shape[1] * k.shape[3] * k.element_size() for k in self.k.values())
+        """Bytes of cache one token takes over all calls (what the declared tensors add up to)."""
+        return sum(t.shape[1] * t.shape[3] * t.element_size() for ts in self.tensors.values() for t in ts.values())
 
     # ---------------------------------------------------------- step views
     def paged_view(self, call: int, batch: StepBatch):
         if call not in self.call_group:
             return None
         owner = self.call_owner[call]
-        return PagedView(self.k[owner], self.v[owner], batch.groups[self.call_group[call]], write=(owner == call))
+        return PagedView(self.tensors[owner], batch.groups[self.call_group[call]], write=(owner == call))
 
     def state_tensor(self, call: int):
         return self.state.get(call)
@@ -159,7 +183,7 @@ class ModelCache:
             width = lay.table_width[g]
             groups.append(GroupView(slots=sl(lay.off_slots[g], T),
                                     block_table=sl(lay.off_table[g], R * width).view(R, width),
-                                    page_size=self.page_size, window=w))
+                                    page_size=self.group_page_size[g], window=w))
         return StepBatch(num_tokens=T, num_requests=R, tokens=sl(lay.off_tokens, T),
                          positions=sl(lay.off_positions, T), token_req=sl(lay.off_token_req, T),
                          cu_q=sl(lay.off_cu_q, R + 1), kv_len=sl(lay.off_kv_len, R),

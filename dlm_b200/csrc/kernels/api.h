@@ -39,10 +39,11 @@ bool gemm_tc_enabled();
 void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, int width, int dtype,
                  cudaStream_t stream);
 
-// Rotates q and k heads of qkv[T, (nh + 2 nkv) * hd] (f32) by position * inv_freq (split-half pairs within the
-// first rotary_dim dims; inv_freq == nullptr: no rotation), writes q to q_out[T, nh * hd] and, where
-// slots != nullptr and slots[t] >= 0, k and v to the paged caches [pages, nkv, page_size, hd].
-void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim,
+// Rotates q and k heads of qkv[T, (nh + 2 nkv) * hd] (f32) by position * inv_freq within the first rotary_dim
+// dims (pair i is dims (i, i + rotary_dim / 2), or (2i, 2i + 1) with interleaved != 0; inv_freq == nullptr: no
+// rotation), writes q to q_out[T, nh * hd] and, where slots != nullptr and slots[t] >= 0, k and v to the paged
+// caches [pages, nkv, page_size, hd].
+void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim, int interleaved,
                    const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int T, int nh, int nkv, int hd,
                    int page_size, int total_pages, int dtype, cudaStream_t stream);
 
@@ -56,12 +57,16 @@ void attention(const void* q, const void* k_cache, const void* v_cache, const in
 // Floats of scratch the decode kernel needs for a step of R requests whose longest holds max_kv_len tokens.
 size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 
-// Router: logits = h · w^T (32-bit), softmax over E, top-k (ties: lower index), optional renormalisation.
-// has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).  norm_w != nullptr: h is the 32-bit residual and
-// rmsnorm(h, norm_w, eps) is applied first, in 32-bit (dtype is then the weights' dtype only).
+// Router: logits = h · w^T (32-bit); scores = softmax over E (score_fn 0) or sigmoid of each logit (score_fn 1);
+// the k best scores (ties: lower index; with select_bias[E] the choice is made on score + bias and the weight
+// stays the score); norm != 0: the chosen weights are divided by their sum; all are multiplied by `scale`.
+// has_gate: w has E + 1 rows and gate[t] = sigmoid(h · w[E]).  The input h is: activations of the weights' dtype
+// (default); the 32-bit residual, with rmsnorm(h, norm_w, eps) applied first in 32-bit (norm_w != nullptr); or
+// 32-bit activations that are already normalised (h_is_f32 != 0).  dtype is the weights' dtype.
 // logits: scratch of T * (E + has_gate) floats (the router logits are left there).
 void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
-                 float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream);
+                 float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
+                 int score_fn, float scale, const float* select_bias, cudaStream_t stream);
 
 // Groups the n = T * k (token, choice) pairs by expert: offsets[E + 1], rows[n] = token of each sorted row,
 // dest[n] = sorted row of pair (t, j).
@@ -88,6 +93,10 @@ void sample(const float* logits, int32_t* out, int N, int V, const float* params
 // A device-side error flag kernels set instead of touching memory they must not (a page id outside the pool,
 // an expert id outside the table).  Returns the flag and clears it.
 int take_error_flag();
+
+// Clears what a decode attention launch that ended through a bounded wait's give-up path (error 5) may have
+// left in the split-merge counters, so that later steps merge correctly.  Call after take_error_flag() == 5.
+void reset_decode_merge_counters(cudaStream_t stream);
 
 // Whether the small kernels are launched so that each may start while the one before it ends
 // (programmatic dependent launch; on unless DLM_B200_NO_PDL=1).

@@ -27,7 +27,9 @@ constexpr int WARPS = 4, BKV = 64, ROWS = 16;
 
 // How many blocks of a (request, kv head, pass of heads) have written their partial results: the block that
 // comes last merges them, so no second kernel is needed.  The counters are zero between launches (the last
-// block puts its counter back), so launches must not overlap; MERGE_SLOTS bounds requests x kv heads x passes.
+// block puts its counter back), so launches must not overlap (one stream at a time in a process); a launch that
+// gave up on a wait leaves counters behind, which reset_decode_merge_counters() clears before the next step.
+// MERGE_SLOTS bounds requests x kv heads x passes.
 constexpr int MERGE_SLOTS = 1 << 16;
 __device__ int g_merge_counters[MERGE_SLOTS];
 
@@ -578,6 +580,16 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
 #undef DLM_DECODE
     check_launch("attention_decode_mma");
     if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, n_splits, BF16, stream);
+}
+
+}  // namespace dlmk
+
+namespace dlmk {
+
+void reset_decode_merge_counters(cudaStream_t stream) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_merge_counters) == cudaSuccess && p != nullptr)
+        cudaMemsetAsync(p, 0, sizeof(int) * MERGE_SLOTS, stream);
 }
 
 }  // namespace dlmk

@@ -32,11 +32,11 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                    ptr<const int32_t>(expert_offsets), num_experts, ptr<const float>(bias), ptr<void>(out), ldo, M, N,
                    K, in_dtype, out_dtype, epilogue, fast, st(stream));
     });
-    m.def("rope_kv_write", [](u64 qkv, u64 positions, u64 inv_freq, int rotary_dim, u64 slots, u64 q_out, u64 k_cache,
-                              u64 v_cache, int T, int nh, int nkv, int hd, int page_size, int total_pages, int dtype,
-                              u64 stream) {
+    m.def("rope_kv_write", [](u64 qkv, u64 positions, u64 inv_freq, int rotary_dim, int interleaved, u64 slots,
+                              u64 q_out, u64 k_cache, u64 v_cache, int T, int nh, int nkv, int hd, int page_size,
+                              int total_pages, int dtype, u64 stream) {
         dlmk::rope_kv_write(ptr<const float>(qkv), ptr<const int32_t>(positions), ptr<const float>(inv_freq),
-                            rotary_dim, ptr<const int32_t>(slots), ptr<void>(q_out), ptr<void>(k_cache),
+                            rotary_dim, interleaved, ptr<const int32_t>(slots), ptr<void>(q_out), ptr<void>(k_cache),
                             ptr<void>(v_cache), T, nh, nkv, hd, page_size, total_pages, dtype, st(stream));
     });
     m.def("attention", [](u64 q, u64 k_cache, u64 v_cache, u64 block_table, int table_width, u64 cu_q, u64 kv_len,
@@ -52,10 +52,11 @@ PYBIND11_MODULE(_dlm_kernels, m) {
         return dlmk::attention_scratch_floats(R, nh, nkv, hd, max_kv_len);
     });
     m.def("router_topk", [](u64 h, u64 w, u64 norm_w, float eps, u64 logits, u64 ids, u64 wts, u64 gate, int T, int H,
-                            int E, int k, int norm, int has_gate, int dtype, u64 stream) {
+                            int E, int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,
+                            u64 select_bias, u64 stream) {
         dlmk::router_topk(ptr<const void>(h), ptr<const void>(w), ptr<const float>(norm_w), eps, ptr<float>(logits),
                           ptr<int32_t>(ids), ptr<float>(wts), ptr<float>(gate), T, H, E, k, norm, has_gate, dtype,
-                          st(stream));
+                          h_is_f32, score_fn, scale, ptr<const float>(select_bias), st(stream));
     });
     m.def("moe_permute", [](u64 ids, int n, int k, int E, u64 offsets, u64 rows, u64 dest, u64 stream) {
         dlmk::moe_permute(ptr<const int32_t>(ids), n, k, E, ptr<int32_t>(offsets), ptr<int32_t>(rows),
@@ -82,6 +83,7 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                           st(stream));
     });
     m.def("take_error_flag", &dlmk::take_error_flag);
+    m.def("reset_decode_merge_counters", [](u64 stream) { dlmk::reset_decode_merge_counters(st(stream)); });
     m.def("dep_launch_enabled", &dlmk::dep_launch_enabled);
     m.def("set_dep_launch", &dlmk::set_dep_launch);
 }

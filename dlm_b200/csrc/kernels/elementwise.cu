@@ -161,7 +161,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut
 // threads run over (head, pair) of the q and k heads, over the unrotated dims, and over the v elements.
 template <typename T>
 __global__ void rope_kv_write_kernel(const float* qkv, const int32_t* __restrict__ positions,
-                                     const float* __restrict__ inv_freq, int rotary_dim,
+                                     const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
                                      const int32_t* __restrict__ slots, T* q_out, T* k_cache,
                                      T* v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
                                      int* err) {
@@ -195,21 +195,22 @@ __global__ void rope_kv_write_kernel(const float* qkv, const int32_t* __restrict
     __syncthreads();
     const int rot_heads = nh + nkv;
     const int tpt = blockDim.x * gridDim.y, tid0 = blockIdx.y * blockDim.x + threadIdx.x;
-    // rotated pairs (i, i + half) of every q and k head
+    // rotated pairs of every q and k head: dims (i, i + half), or (2i, 2i + 1) when interleaved
     for (int idx = tid0; idx < rot_heads * half; idx += tpt) {
         const int h = idx / half, i = idx % half;
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
         const float* src = row + (long long)h * hd;          // q heads then k heads are contiguous in qkv
-        const float a = src[i], b = src[i + half];
+        const float a = src[ia], b = src[ib];
         const float sn = sc[i], cs = sc[half + i];
         const float lo = a * cs - b * sn, hi = a * sn + b * cs;
         if (h < nh) {
             T* o = q_out + (long long)t * Q + h * hd;
-            o[i] = from_f32<T>(lo);
-            o[i + half] = from_f32<T>(hi);
+            o[ia] = from_f32<T>(lo);
+            o[ib] = from_f32<T>(hi);
         } else if (page >= 0) {
             T* o = k_cache + (((long long)page * nkv + (h - nh)) * page_size + in_page) * hd;
-            o[i] = from_f32<T>(lo);
-            o[i + half] = from_f32<T>(hi);
+            o[ia] = from_f32<T>(lo);
+            o[ib] = from_f32<T>(hi);
         }
     }
     // dims from rotary_dim on pass through
@@ -234,7 +235,7 @@ __global__ void rope_kv_write_kernel(const float* qkv, const int32_t* __restrict
 // addresses that allow it.  Per element the arithmetic is that of rope_kv_write_kernel.
 template <typename T>
 __global__ void rope_kv_write_vec_kernel(const float* qkv, const int32_t* __restrict__ positions,
-                                         const float* __restrict__ inv_freq, int rotary_dim,
+                                         const float* __restrict__ inv_freq, int rotary_dim, int /*interleaved: never*/,
                                          const int32_t* __restrict__ slots, T* q_out, T* k_cache,
                                          T* v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
                                          int* err) {
@@ -394,7 +395,7 @@ void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int
     check_launch("rmsnorm");
 }
 
-void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim,
+void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim, int interleaved,
                    const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int T, int nh, int nkv, int hd,
                    int page_size, int total_pages, int dtype, cudaStream_t stream) {
     if (T <= 0) return;
@@ -407,7 +408,7 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
     if (T >= 512) slices = 1; else if (slices > 16) slices = 16;
     const size_t smem = inv_freq != nullptr ? sizeof(float) * rotary_dim : 0;
     const int half = inv_freq != nullptr ? rotary_dim / 2 : 0;
-    const bool vec = hd % 4 == 0 && half % 4 == 0 &&
+    const bool vec = hd % 4 == 0 && half % 4 == 0 && !interleaved &&
                      ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                        reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
     if (vec) {
@@ -417,12 +418,12 @@ void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_
     dim3 grid(T, slices);
     if (dtype == F32) {
         auto kern = vec ? rope_kv_write_vec_kernel<float> : rope_kv_write_kernel<float>;
-        launch_dep(kern, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
+        launch_dep(kern, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, interleaved, slots,
             static_cast<float*>(q_out), static_cast<float*>(k_cache), static_cast<float*>(v_cache), nh, nkv, hd,
             page_size, total_pages, err);
     } else {
         auto kern = vec ? rope_kv_write_vec_kernel<__nv_bfloat16> : rope_kv_write_kernel<__nv_bfloat16>;
-        launch_dep(kern, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, slots,
+        launch_dep(kern, grid, threads, smem, stream, qkv, positions, inv_freq, rotary_dim, interleaved, slots,
             static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
             static_cast<__nv_bfloat16*>(v_cache), nh, nkv, hd, page_size, total_pages, err);
     }

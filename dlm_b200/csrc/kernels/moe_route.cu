@@ -168,11 +168,14 @@ router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __
     }
 }
 
-// Softmax over the experts, top-k (ties: lower index), optional renormalisation, the shared expert's
-// sigmoid gate.  One warp per token.
+// Scores from the logits (score_fn 0: softmax over the experts; 1: a sigmoid of each logit), the k best
+// (ties: lower index; with select_bias the choice is made on score + bias, the weight stays the score),
+// optional renormalisation of the chosen weights, a constant factor, and the shared expert's sigmoid gate.
+// One warp per token.
 __global__ void __launch_bounds__(128)
 router_select_kernel(const float* logits, int32_t* ids, float* wts,
-                     float* gate, int T, int E, int k, int norm, int has_gate) {
+                     float* gate, int T, int E, int k, int norm, int has_gate, int score_fn, float scale,
+                     const float* __restrict__ select_bias) {
     extern __shared__ float smem[];
     dep_wait();
     dep_launch_next();
@@ -180,30 +183,36 @@ router_select_kernel(const float* logits, int32_t* ids, float* wts,
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= T) return;
     const int rows = E + (has_gate ? 1 : 0);
-    float* prob = smem + warp * (E + 1);
+    float* prob = smem + warp * 2 * (E + 1);     // the scores
+    float* pick = prob + (E + 1);                // what the choice is made on (score, or score + bias)
     for (int e = lane; e < rows; e += 32) prob[e] = logits[(long long)t * rows + e];
     __syncwarp();
     if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-prob[E]));
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float p = expf(prob[e] - mx);
-        prob[e] = p;
-        sum += p;
+    if (score_fn == 0) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, prob[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(prob[e] - mx);
+            prob[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        if (sum > 0.f)
+            for (int e = lane; e < E; e += 32) prob[e] = prob[e] / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) prob[e] = 1.0f / (1.0f + expf(-prob[e]));
     }
-    sum = warp_sum(sum);
-    __syncwarp();
-    if (sum > 0.f)
-        for (int e = lane; e < E; e += 32) prob[e] = prob[e] / sum;
+    for (int e = lane; e < E; e += 32) pick[e] = prob[e] + (select_bias != nullptr ? select_bias[e] : 0.f);
     __syncwarp();
     float chosen_sum = 0.f;
     for (int j = 0; j < k; ++j) {
-        float bv = -1.f;
+        float bv = -INFINITY;
         int bi = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float p = prob[e];
+            const float p = pick[e];
             if (p > bv) { bv = p; bi = e; }     // ascending e per lane: ties keep the lower index
         }
 #pragma unroll
@@ -212,16 +221,21 @@ router_select_kernel(const float* logits, int32_t* ids, float* wts,
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
+        const float w = prob[bi];               // every lane reads it before lane 0 marks the expert as taken
+        __syncwarp();
         if (lane == 0) {
             ids[t * k + j] = bi;
-            wts[t * k + j] = bv;
-            prob[bi] = -2.f;                    // taken
+            wts[t * k + j] = w;
+            pick[bi] = -INFINITY;               // taken
         }
-        chosen_sum += bv;
+        chosen_sum += w;
         __syncwarp();
     }
-    if (norm && chosen_sum > 0.f && lane == 0)
-        for (int j = 0; j < k; ++j) wts[t * k + j] = wts[t * k + j] / chosen_sum;
+    if (lane == 0) {
+        const float div = (norm && chosen_sum > 0.f) ? chosen_sum : 1.0f;
+        if (div != 1.0f || scale != 1.0f)
+            for (int j = 0; j < k; ++j) wts[t * k + j] = (wts[t * k + j] / div) * scale;
+    }
 }
 
 constexpr int PERMUTE_THREADS = 1024;
@@ -268,8 +282,11 @@ moe_permute_kernel(const int32_t* ids, int n, int k, int E, int32_t* offsets,
 }  // namespace
 
 void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
-                 float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, cudaStream_t stream) {
+                 float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
+                 int score_fn, float scale, const float* select_bias, cudaStream_t stream) {
     if (T <= 0) return;
+    DLM_CHECK(score_fn == 0 || score_fn == 1, "router: score function must be 0 (softmax) or 1 (sigmoid)");
+    const bool x32 = norm_w != nullptr || h_is_f32 != 0;      // the activations are 32-bit whatever the weights are
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
     const size_t smem = sizeof(float) * (size_t)H;
     DLM_CHECK(smem <= 200 * 1024, "router: hidden_size does not fit in shared memory");
@@ -288,7 +305,7 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
                    static_cast<const TW*>(w), norm_w, eps, logits, T, H, rows);                               \
     }
         if (dtype == F32) DLM_ROUTER_MULTI(float, float)
-        else if (norm_w != nullptr) DLM_ROUTER_MULTI(float, __nv_bfloat16)
+        else if (x32) DLM_ROUTER_MULTI(float, __nv_bfloat16)
         else DLM_ROUTER_MULTI(__nv_bfloat16, __nv_bfloat16)
 #undef DLM_ROUTER_MULTI
         check_launch("router_logits_multi");
@@ -303,16 +320,16 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
     }
     // with norm_w the activations are the 32-bit residual whatever the weights' dtype
     if (dtype == F32) { if (vec) DLM_ROUTER(float, float, true) else DLM_ROUTER(float, float, false) }
-    else if (norm_w != nullptr) { if (vec) DLM_ROUTER(float, __nv_bfloat16, true) else DLM_ROUTER(float, __nv_bfloat16, false) }
+    else if (x32) { if (vec) DLM_ROUTER(float, __nv_bfloat16, true) else DLM_ROUTER(float, __nv_bfloat16, false) }
     else { if (vec) DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER(__nv_bfloat16, __nv_bfloat16, false) }
 #undef DLM_ROUTER
     check_launch("router_logits");
     }
     const int wpb = 4;
-    const size_t smem2 = sizeof(float) * (size_t)wpb * (E + 1);
+    const size_t smem2 = sizeof(float) * (size_t)wpb * 2 * (E + 1);
     cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     launch_dep(router_select_kernel, (T + wpb - 1) / wpb, wpb * 32, smem2, stream, logits, ids, wts, gate, T, E, k,
-               norm, has_gate);
+               norm, has_gate, score_fn, scale, select_bias);
     check_launch("router_select");
 }
 

@@ -10,6 +10,7 @@ budget and decoded tokens of other requests share the step.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Iterable, Sequence
 
 import torch
@@ -57,11 +58,13 @@ class Engine:
         self.scheduler = host.Scheduler(self.cache.manager, host.SchedulerConfig(
             max_step_tokens=int(max_step_tokens), max_step_requests=int(max_requests),
             max_context=self.max_context, vocab_size=int(model.spec.vocab_size)))
-        # replayed CUDA graphs of pure decode steps, keyed by (rows, bucket of the longest request)
-        # (not for models with per-request state: building a graph runs its step once more)
+        # replayed CUDA graphs of pure decode steps, keyed by (rows, bucket of the longest request); at most
+        # `max_graphs` are kept, the least recently used goes first.  Not for a model with a part that
+        # synchronises with the host inside its forward.
         self.use_graphs = (self.rt.device.type == "cuda" and hasattr(self.rt.ops, "launches")
-                           and not self.cache.state)
-        self._graphs: dict[tuple[int, int], dict] = {}
+                           and all(part.graph_safe for part in self._all_parts()))
+        self.max_graphs = 32
+        self._graphs: "OrderedDict[tuple[int, int], dict]" = OrderedDict()
         self._graph_pool = None
         self._samplers: dict[int, RequestSampler] = {}
         self._results: dict[int, list[int]] = {}
@@ -82,12 +85,18 @@ class Engine:
         cfg, model = random_model(config, seed, rt)
         return cls(cfg, model, **kw)
 
+    def _all_parts(self):
+        for block in self.model.blocks:
+            yield block
+            for _, part in block.children():
+                yield part
+
     def _tokens_that_fit(self, page_size: int) -> int:
         per_token = 0
-        for kv, _, owner in self.model.cache_needs():
-            if kv is not None:
-                per_token += 2 * kv.num_kv_heads * kv.head_dim * (2 if self.rt.dtype == torch.bfloat16 else 4)
-        per_token = max(per_token // 1, 1)
+        for ci, (need, _, owner) in enumerate(self.model.cache_needs()):
+            if need is not None and owner == ci:
+                per_token += need.elements_per_token() * (2 if self.rt.dtype == torch.bfloat16 else 4)
+        per_token = max(per_token, 1)
         if self.rt.device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(self.rt.device)
             budget = int(free * 0.6)
@@ -109,53 +118,51 @@ class Engine:
         return self.model.step(batch, self.cache)
 
     # ------------------------------------------------- replayed decode steps
-    def _decode_graph(self, rows: int, bucket: int, items) -> dict:
-        """The captured graph of a decode step of `rows` requests none of which holds more than
-        `bucket` tokens: the step function and the arg-max over its logits.  Everything the kernels
-        read that changes from step to step lies in one device buffer of fixed layout."""
-        key = (rows, bucket)
+    def _run_decode(self, items):
+        """A pure decode step through its graph.  Returns (logits, greedy tokens) on the device.
+
+        A graph is the step function and the arg-max over its logits for `rows` requests none of which
+        holds more than `bucket` tokens; everything its kernels read that changes from step to step lies
+        in one device buffer of fixed layout, refilled before every replay.  The first step of a new
+        (rows, bucket) runs eagerly on that buffer (first-call set-up of the kernels must not fall into a
+        capture) and its result is the step's result; the graph is then recorded for the steps after it.
+        Recording runs nothing, so every step runs exactly once, which per-request state needs."""
+        cache, ops = self.cache, self.rt.ops
+        longest = max(cache.manager.length(s) for s, _, _ in items)
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        bucket = min(bucket, max(self.max_context, longest))
+        key = (len(items), bucket)
+        sitems = [cache.host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
         ent = self._graphs.get(key)
         if ent is not None:
-            return ent
-        cache, ops = self.cache, self.rt.ops
-        width = -(-self.max_context // cache.page_size)
-        host = cache.host
-        sitems = [host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
+            self._graphs.move_to_end(key)
+            cache.fill_metadata(sitems, ent["layout"], ent["meta"])
+            ent["graph"].replay()
+            ops.launches += ent["launches"]
+            return ent["logits"], ent["tokens"]
+        width = -(-self.max_context // min(cache.group_page_size))
         lay = cache.manager.plan_layout(sitems, width)
         meta = torch.zeros(lay.total, dtype=torch.int32, device=self.rt.device)
         batch = cache.batch_from_layout(lay, meta)
         batch.max_kv_len = bucket
         cache.fill_metadata(sitems, lay, meta)
-        # once eagerly (first-call set-up of the kernels must not fall into the capture), then capture
-        torch.cuda.synchronize()
-        ops.argmax(self.model.step(batch, cache))
+        logits = self.model.step(batch, cache)
+        tokens = ops.argmax(logits)
         torch.cuda.synchronize()
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
         with torch.cuda.graph(graph, pool=self._graph_pool):
-            logits = self.model.step(batch, cache)
-            tokens = ops.argmax(logits)
-        ent = dict(graph=graph, layout=lay, meta=meta, logits=logits, tokens=tokens,
-                   launches=ops.launches - before, width=width)
-        self._graphs[key] = ent
-        return ent
-
-    def _run_decode(self, items):
-        """A pure decode step through its graph.  Returns (logits, greedy tokens) on the device."""
-        longest = max(self.cache.manager.length(s) for s, _, _ in items)
-        bucket = 256
-        while bucket < longest:
-            bucket *= 2
-        bucket = min(bucket, max(self.max_context, longest))
-        ent = self._decode_graph(len(items), bucket, items)
-        host = self.cache.host
-        sitems = [host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
-        self.cache.fill_metadata(sitems, ent["layout"], ent["meta"])
-        ent["graph"].replay()
-        self.rt.ops.launches += ent["launches"]
-        return ent["logits"], ent["tokens"]
+            g_logits = self.model.step(batch, cache)
+            g_tokens = ops.argmax(g_logits)
+        while len(self._graphs) >= self.max_graphs:
+            self._graphs.popitem(last=False)
+        self._graphs[key] = dict(graph=graph, layout=lay, meta=meta, logits=g_logits, tokens=g_tokens,
+                                 launches=ops.launches - before, width=width)
+        return logits, tokens
 
     # ------------------------------------------------------------- generation
     def submit(self, prompt: Iterable[int], params: SamplingParams | None = None, max_new_tokens: int = 16,

@@ -95,6 +95,9 @@ class NativeOps:
     def check_errors(self) -> None:
         """Raises if a kernel refused an access (page or token id outside its table)."""
         flag = self.k.take_error_flag()
+        if flag == 5:
+            # a kernel gave up on a wait: the decode attention's split counters may not be back at zero
+            self.k.reset_decode_merge_counters(self._stream())
         if flag:
             what = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
                     3: "a visible key has no page", 4: "expert id outside the table",
@@ -168,14 +171,17 @@ class NativeOps:
         return out
 
     # ------------------------------------------------------------- attention
-    def rope_kv_write(self, qkv, positions, inv_freq, rotary_dim, slots, k_cache, v_cache, nh, nkv, hd, out_dtype):
+    def rope_kv_write(self, qkv, positions, inv_freq, rotary_dim, slots, k_cache, v_cache, nh, nkv, hd, out_dtype,
+                      interleaved=False):
+        """``interleaved``: rotary pairs are dims (2i, 2i + 1) instead of (i, i + rotary_dim / 2)."""
         T = qkv.shape[0]
         assert qkv.dtype == torch.float32 and qkv.shape[1] == (nh + 2 * nkv) * hd
         total_pages, nkv_c, page_size, hd_c = k_cache.shape
         assert (nkv_c, hd_c) == (nkv, hd) and k_cache.dtype == out_dtype
         q = torch.empty((T, nh * hd), dtype=out_dtype, device=qkv.device)
         self.launches += 1
-        self.k.rope_kv_write(_p(qkv), _p(positions), _p(inv_freq), int(rotary_dim), _p(slots), _p(q), _p(k_cache),
+        self.k.rope_kv_write(_p(qkv), _p(positions), _p(inv_freq), int(rotary_dim), int(bool(interleaved)), _p(slots),
+                             _p(q), _p(k_cache),
                              _p(v_cache), T, nh, nkv, hd, page_size, total_pages, _dt(out_dtype), self._stream())
         return q
 
@@ -199,18 +205,25 @@ class NativeOps:
         return out
 
     # ------------------------------------------------------------------- moe
-    def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0):
-        """With ``norm_weight`` given, ``h`` is the 32-bit residual and the RMS norm runs inside the kernel."""
+    def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
+                    select_bias=None):
+        """Scores (``score``: softmax over the experts, or a sigmoid of each logit), the k best (chosen on
+        score + ``select_bias`` when that is given), optionally renormalised, times ``scale``.  ``h`` is one
+        of: activations in the weights' dtype; the 32-bit residual together with ``norm_weight`` / ``eps``
+        (the RMS norm then runs inside the kernel, in 32-bit); 32-bit activations that are already normalised."""
         T, H = h.shape
         assert w.shape == (E + (1 if has_gate else 0), H)
-        assert (norm_weight is None and h.dtype == w.dtype) or (norm_weight is not None and h.dtype == torch.float32)
+        assert h.dtype in (w.dtype, torch.float32) and (norm_weight is None or h.dtype == torch.float32)
+        score_fn = {"softmax": 0, "sigmoid": 1}[score]
+        h_is_f32 = int(norm_weight is None and h.dtype == torch.float32 and w.dtype != torch.float32)
         ids = torch.empty((T, k), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, k), dtype=torch.float32, device=h.device)
         gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
         logits = torch.empty((T, w.shape[0]), dtype=torch.float32, device=h.device)
         self.launches += 2
         self.k.router_topk(_p(h), _p(w), _p(norm_weight), float(eps), _p(logits), _p(ids), _p(wts), _p(gate), T, H,
-                           E, k, int(norm), int(has_gate), _dt(w.dtype), self._stream())
+                           E, k, int(norm), int(has_gate), _dt(w.dtype), h_is_f32, score_fn, float(scale),
+                           _p(select_bias), self._stream())
         return ids, wts, gate
 
     def moe_permute(self, ids, E):

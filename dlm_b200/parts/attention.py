@@ -70,7 +70,8 @@ class GroupedQueryAttention(Mixer):
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
         q = ops.rope_kv_write(qkv, b.positions, inv_freq, rotary_dim,
                               view.group.slots if view.write else None,
-                              view.k, view.v, self.nh, self.nkv, self.hd, rt.dtype)
+                              view.k, view.v, self.nh, self.nkv, self.hd, rt.dtype,
+                              interleaved=bool(rot is not None and self.position.interleaved))
         o = ops.attention(q, view.k, view.v, view.group.block_table, b.cu_q, b.kv_len,
                           self.window or 0, self.scale, self.nh, self.nkv, self.hd,
                           b.max_q_len, b.max_kv_len, b.num_single)

@@ -4,7 +4,7 @@ A *part* has its sizes and constants as constructor parameters and never
 learns which model it is in.  It names its tensors relative to itself
 (``q_proj.weight``); the model prefixes them.  Four kinds of part exist:
 
-* ``Norm``              ``forward(x_f32, rt, rows=None) -> activations``
+* ``Norm``              ``forward(x_f32, rt, rows=None, out_dtype=None) -> activations``
 * ``PositionEncoding``  gives the rotation table the attention kernels apply
 * ``Mixer``             ``forward(h, resid, ctx, call)``: adds its output to ``resid``
 * ``FeedForward``       ``forward(h, resid, ctx, pre_norm)``: adds its output to ``resid``
@@ -35,12 +35,36 @@ class ParamSpec:
 
 
 @dataclass(frozen=True)
-class PagedKV:
-    """A mixer's need for cached keys and values: per token ``num_kv_heads * head_dim``
-    keys and as many values; ``window`` None keeps all of them, W keeps the last W."""
-    num_kv_heads: int
-    head_dim: int
+class CacheTensor:
+    """One paged tensor of a mixer's cache: per token ``heads`` rows of ``width`` elements,
+    laid out ``[pages, heads, page_size, width]``."""
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
+class PagedCache:
+    """What a mixer wants cached per token, in pages: any number of tensors (keys and values, or
+    one latent vector, ...).  ``window`` None keeps every token, W keeps the last W (older pages go
+    back to the pool).  ``page_size`` None takes the engine's page size; layers whose window and
+    page size agree share a pool of pages and a block table."""
+    tensors: tuple[CacheTensor, ...]
     window: int | None = None
+    page_size: int | None = None
+
+    def elements_per_token(self) -> int:
+        return sum(t.heads * t.width for t in self.tensors)
+
+    def same_layout(self, other: "PagedCache") -> bool:
+        return self.tensors == other.tensors and self.page_size == other.page_size
+
+
+def PagedKV(num_kv_heads: int, head_dim: int, window: int | None = None, page_size: int | None = None) -> PagedCache:
+    """The need of an attention mixer: per token ``num_kv_heads * head_dim`` keys (tensor ``k``)
+    and as many values (tensor ``v``)."""
+    return PagedCache((CacheTensor("k", int(num_kv_heads), int(head_dim)),
+                       CacheTensor("v", int(num_kv_heads), int(head_dim))), window, page_size)
 
 
 @dataclass(frozen=True)
@@ -77,6 +101,10 @@ class Runtime:
 
 
 class Part:
+    # False for a part whose forward reads device data on the host (a synchronisation): steps of a
+    # model that holds one are not captured in CUDA graphs.
+    graph_safe = True
+
     def param_specs(self) -> list[ParamSpec]:
         return []
 
@@ -86,14 +114,26 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, x: torch.Tensor, rt: Runtime, rows: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, rt: Runtime, rows: torch.Tensor | None = None,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """Normalises the 32-bit rows ``x`` (only ``rows`` of them when given); the result has
+        ``out_dtype``, the runtime's activation dtype when None."""
         raise NotImplementedError
+
+    def fusable_rms(self) -> tuple[torch.Tensor, float] | None:
+        """``(weight, eps)`` if this norm is a plain RMS norm that a kernel may apply itself to the
+        32-bit residual (the router's kernel does), else None: the caller then asks ``forward`` for a
+        32-bit result."""
+        return None
 
 
 class PositionEncoding(Part):
     """``rotary()`` returns None or ``(inv_freq f32[rotary_dim/2] on the device, rotary_dim)``:
-    dimension pairs ``(i, i + rotary_dim/2)`` of each head are rotated by
-    ``position * inv_freq[i]``; dimensions from ``rotary_dim`` on pass through."""
+    pair i of each head is rotated by ``position * inv_freq[i]``; dimensions from ``rotary_dim``
+    on pass through.  Pair i is dims ``(i, i + rotary_dim/2)``, or ``(2i, 2i + 1)`` when the
+    class attribute ``interleaved`` is True."""
+
+    interleaved = False
 
     def rotary(self, rt: Runtime):
         return None
@@ -103,7 +143,7 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_need(self) -> PagedKV | None:
+    def cache_need(self) -> PagedCache | None:
         return None
 
     def state_need(self) -> RequestState | None:
@@ -150,10 +190,17 @@ class StepBatch:
 
 @dataclass
 class PagedView:
-    k: torch.Tensor             # [pages, num_kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    tensors: dict[str, torch.Tensor]   # by CacheTensor.name: [pages, heads, page_size, width]
     group: GroupView
     write: bool                 # False when this call only reads another call's cache
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.tensors["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.tensors["v"]
 
 
 class StepContext:

@@ -5,7 +5,6 @@ import torch
 
 from ..registry import register_part
 from .base import FeedForward, ParamSpec, Runtime, StepContext
-from .norm import RMSNorm
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -105,12 +104,15 @@ class SoftmaxTopKMoE(FeedForward):
             with branch:
                 sact = ops.linear_swiglu(h, self.ws_gate_up)
                 shared = ops.linear(sact, self.ws_down, None, torch.float32)
-        if isinstance(pre_norm, RMSNorm):
-            # router logits (and the shared expert's gate) from the 32-bit normalised residual
+        # router logits (and the shared expert's gate) from the 32-bit normalised residual: an RMS norm is
+        # applied again inside the router's kernel, any other norm is asked for a 32-bit result
+        rms = pre_norm.fusable_rms() if pre_norm is not None else None
+        if rms is not None:
             ids, wts, gate = ops.router_topk(resid, self.w_router, self.E, self.k, self.norm, self.has_gate,
-                                             norm_weight=pre_norm.weight, eps=pre_norm.eps)
+                                             norm_weight=rms[0], eps=rms[1])
         else:
-            ids, wts, gate = ops.router_topk(h, self.w_router, self.E, self.k, self.norm, self.has_gate)
+            x = h if pre_norm is None else pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)
+            ids, wts, gate = ops.router_topk(x, self.w_router, self.E, self.k, self.norm, self.has_gate)
         offsets, rows, dest = ops.moe_permute(ids, self.E)
         act = ops.grouped_swiglu(h, self.w_gate_up, offsets, rows)
         y = ops.grouped_linear(act, self.w_down, offsets)

@@ -71,7 +71,7 @@ class DecoderModel:
                     raise ValueError(f"call {ci} must read the cache of an earlier call that owns one")
                 a = self.blocks[c.layer].mixer.cache_need()
                 b = self.blocks[self.order[c.reads_cache_of].layer].mixer.cache_need()
-                if a is None or b is None or (a.num_kv_heads, a.head_dim) != (b.num_kv_heads, b.head_dim):
+                if a is None or b is None or not a.same_layout(b):
                     raise ValueError(f"call {ci} cannot read call {c.reads_cache_of}'s cache: their shapes differ")
         self.embed: torch.Tensor | None = None
         self.lm_head: torch.Tensor | None = None
@@ -119,7 +119,7 @@ class DecoderModel:
 
     # --------------------------------------------------------------- cache
     def cache_needs(self):
-        """Per call of the order: (PagedKV or None, RequestState or None, owner call index)."""
+        """Per call of the order: (PagedCache or None, RequestState or None, owner call index)."""
         out = []
         for ci, c in enumerate(self.order):
             mixer = self.blocks[c.layer].mixer

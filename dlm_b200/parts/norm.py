@@ -21,8 +21,11 @@ class RMSNorm(Norm):
     def load(self, tensors, rt: Runtime):
         self.weight = rt.vector(tensors["weight"])
 
-    def forward(self, x, rt: Runtime, rows=None):
-        return rt.ops.rmsnorm(x, self.weight, self.eps, rt.dtype, rows)
+    def forward(self, x, rt: Runtime, rows=None, out_dtype=None):
+        return rt.ops.rmsnorm(x, self.weight, self.eps, out_dtype or rt.dtype, rows)
+
+    def fusable_rms(self):
+        return self.weight, self.eps
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -36,9 +36,16 @@ class RotaryNeoX(PositionEncoding):
         return self._table, self.rotary_dim
 
 
+class RotaryInterleaved(RotaryNeoX):
+    """The same rotation on neighbouring pairs ``(2i, 2i + 1)`` of every head."""
+
+    interleaved = True
+
+
 class NoPositionEncoding(PositionEncoding):
     """Keys and queries are used as projected."""
 
 
 register_part("position", "rope_neox", RotaryNeoX)
+register_part("position", "rope_interleaved", RotaryInterleaved)
 register_part("position", "none", NoPositionEncoding)

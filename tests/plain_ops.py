@@ -82,7 +82,8 @@ class PlainOps:
         return out
 
     # ------------------------------------------------------------- attention
-    def rope_kv_write(self, qkv, positions, inv_freq, rotary_dim, slots, k_cache, v_cache, nh, nkv, hd, out_dtype):
+    def rope_kv_write(self, qkv, positions, inv_freq, rotary_dim, slots, k_cache, v_cache, nh, nkv, hd, out_dtype,
+                      interleaved=False):
         T = qkv.shape[0]
         Q, KV = nh * hd, nkv * hd
         q = qkv[:, :Q].reshape(T, nh, hd).clone()
@@ -93,9 +94,14 @@ class PlainOps:
             ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
             sin, cos = torch.sin(ang)[:, None, :], torch.cos(ang)[:, None, :]
             for x in (q, k):
-                a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
-                x[..., :half] = a * cos - b * sin
-                x[..., half:rotary_dim] = a * sin + b * cos
+                if interleaved:
+                    a, b = x[..., 0:rotary_dim:2].clone(), x[..., 1:rotary_dim:2].clone()
+                    x[..., 0:rotary_dim:2] = a * cos - b * sin
+                    x[..., 1:rotary_dim:2] = a * sin + b * cos
+                else:
+                    a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+                    x[..., :half] = a * cos - b * sin
+                    x[..., half:rotary_dim] = a * sin + b * cos
         if slots is not None:
             ps = k_cache.shape[2]
             sl = slots.long()
@@ -136,7 +142,8 @@ class PlainOps:
         return out.to(q.dtype)
 
     # ------------------------------------------------------------------- moe
-    def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0):
+    def router_topk(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
+                    select_bias=None):
         if norm_weight is not None:
             h = self.rmsnorm(h, norm_weight, eps, torch.float32)
         logits = _f(h) @ _f(w).T
@@ -144,13 +151,14 @@ class PlainOps:
         if has_gate:
             gate = 1.0 / (1.0 + torch.exp(-logits[:, E]))
             logits = logits[:, :E]
-        probs = torch.softmax(logits, dim=-1)
-        ids = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :k]
+        probs = torch.softmax(logits, dim=-1) if score == "softmax" else 1.0 / (1.0 + torch.exp(-logits))
+        pick = probs if select_bias is None else probs + select_bias[None, :].to(probs.dtype)
+        ids = torch.sort(pick, dim=-1, descending=True, stable=True).indices[:, :k]
         wts = torch.gather(probs, 1, ids)
         if norm:
             s = wts.sum(-1, keepdim=True)
             wts = torch.where(s > 0, wts / s, wts)
-        return ids.to(torch.int32), wts, gate
+        return ids.to(torch.int32), wts * scale, gate
 
     def moe_permute(self, ids, E):
         T, k = ids.shape

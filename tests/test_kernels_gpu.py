@@ -172,6 +172,26 @@ def test_router(ops, ref, dtype, E, k, H, norm, gate):
     close(a[1], b[1], rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("E,k,H,norm,score,scale,bias", [
+    (8, 2, 64, True, "sigmoid", 1.5, True), (12, 3, 256, False, "sigmoid", 1.0, False),
+    (60, 4, 2048, True, "softmax", 2.5, True), (130, 6, 100, False, "softmax", 0.5, True)])
+def test_router_score_functions(ops, ref, dtype, E, k, H, norm, score, scale, bias):
+    """Sigmoid scores, a selection bias that moves the choice but not the weights, a scale factor; and the
+    input given as 32-bit activations that are already normalised (weights in the other dtype)."""
+    T = 23
+    x32 = rand((T, H), torch.float32, 24)
+    w = rand((E, H), dtype, 25, 0.3)
+    b = rand((E,), torch.float32, 26, 0.2) if bias else None
+    got = ops.router_topk(x32, w, E, k, norm, False, score=score, scale=scale, select_bias=b)
+    want = ref.router_topk(x32, w, E, k, norm, False, score=score, scale=scale, select_bias=b)
+    assert torch.equal(got[0], want[0])
+    close(got[1], want[1], rtol=1e-4, atol=1e-6)
+    if bias:        # the bias changed some choices, or the case shows nothing
+        plain = ref.router_topk(x32, w, E, k, norm, False, score=score, scale=scale)
+        assert not torch.equal(plain[0], want[0])
+
+
 def test_router_hand_values_and_ties(ops):
     # src/forward/cpu.rs:1580-1595: logits [1, 2, 0], top-2 -> experts [1, 0]; renormalised weights sum to 1
     h = torch.eye(3, device="cuda")[:1]                     # picks column 0 of w^T
@@ -210,6 +230,28 @@ def test_rope_kv_write(ops, ref, dtype, nh, nkv, hd, rd):
     q3 = ops.rope_kv_write(qkv, pos, None, 0, None, k3, k3.clone(), nh, nkv, hd, dtype)
     close(q3, qkv[:, :nh * hd].to(dtype), rtol=0, atol=0)
     assert float(k3.abs().max()) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rd", [(4, 2, 16, 16), (3, 1, 48, 24), (2, 2, 128, 128)])
+def test_rope_interleaved_pairs(ops, ref, dtype, nh, nkv, hd, rd):
+    from dlm_b200.parts.rope import rope_inv_freqs
+    T, ps, pages = 7, 16, 3
+    qkv = rand((T, (nh + 2 * nkv) * hd), torch.float32, 18)
+    pos = torch.tensor([0, 1, 2, 50, 1000, 4095, 7], dtype=torch.int32, device="cuda")
+    slots = torch.tensor([0, 1, 17, 40, 33, -1, 15], dtype=torch.int32, device="cuda")
+    inv = rope_inv_freqs(hd, 10000.0, rd).cuda()
+    k1 = torch.zeros((pages, nkv, ps, hd), dtype=dtype, device="cuda")
+    v1, k2, v2 = k1.clone(), k1.clone(), k1.clone()
+    q1 = ops.rope_kv_write(qkv, pos, inv, rd, slots, k1, v1, nh, nkv, hd, dtype, interleaved=True)
+    q2 = ref.rope_kv_write(qkv, pos, inv, rd, slots, k2, v2, nh, nkv, hd, dtype, interleaved=True)
+    t = dict(rtol=1e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    close(q1, q2, **t)
+    close(k1, k2, **t)
+    close(v1, v2, rtol=0, atol=0)
+    # and it is another rotation than the split-half one
+    q3 = ref.rope_kv_write(qkv, pos, inv, rd, None, k2, v2, nh, nkv, hd, dtype)
+    assert float((q3.float() - q2.float()).abs().max()) > 0.1
 
 
 def test_rope_identity_at_zero_and_norm(ops):

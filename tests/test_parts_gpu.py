@@ -40,7 +40,7 @@ class OneLayerCache:
                                positions=i32(list(range(tokens))), token_req=i32([0] * tokens), cu_q=i32([0, tokens]),
                                kv_len=i32([tokens]), state_slot=i32([0]), logit_rows=i32([]), groups=[group],
                                max_q_len=tokens, max_kv_len=tokens, num_single=0)
-        self.view = PagedView(self.k, self.v, group, write=True)
+        self.view = PagedView({"k": self.k, "v": self.v}, group, write=True)
 
     def context(self, rt):
         from dlm_b200.parts.base import StepContext

@@ -62,6 +62,10 @@ def test_replayed_decode_steps_give_the_oracles_logits(name, page_size, dtype, t
         for row, (rid, tok) in enumerate(produced):
             got[rid].append((tok, logits[row]))
             replayed[rid].append(from_graph)
+    # every decode step is replayed from a graph except the first of each (rows, bucket), which runs eagerly
+    # and is then recorded; both kinds are compared below
+    decode_steps = [f for r in replayed.values() for f in r[1:]]
+    assert sum(decode_steps) >= len(decode_steps) - 3 * len(eng._graphs) and sum(decode_steps) > len(decode_steps) // 2
     buckets = sorted({k[1] for k in eng._graphs})
     rows_seen = sorted({k[0] for k in eng._graphs})
     assert buckets == [256, 512] and rows_seen == [1, 2, 3], (buckets, rows_seen)
@@ -69,7 +73,6 @@ def test_replayed_decode_steps_give_the_oracles_logits(name, page_size, dtype, t
     for rid, p, n in zip(ids, prompts, news):
         out = [t for t, _ in got[rid]]
         assert out == eng.result(rid) and len(out) == n
-        assert all(replayed[rid][1:]), "decode steps after the first token must be replayed graphs"
         toks = p + out[:-1]
         ref, margins = oracle.logits(toks), oracle.router_margins(toks)
         rows = {len(p) - 1 + i: row for i, (_, row) in enumerate(got[rid])}

@@ -37,15 +37,22 @@ def define_toy():
             ops, b = ctx.rt.ops, ctx.batch
             state = ctx.state(call)                                   # [slots, n]
             u = ops.linear(h, self.w_in, None, torch.float32)         # [T, n]
-            cu, slots = b.cu_q.tolist(), b.state_slot.tolist()
-            s_all = torch.empty_like(u)
-            for r, slot in enumerate(slots):                          # a plain scan: this is a toy
-                s = state[slot]
-                for t in range(cu[r], cu[r + 1]):
-                    s = self.decay * s + u[t]
-                    s_all[t] = s
-                state[slot] = s
-            ops.linear_add(s_all.to(ctx.rt.dtype), self.w_out, resid)
+            T = u.shape[0]
+            # A scan over the portion, all requests side by side, without reading anything on the host
+            # (so that the step can be recorded in a CUDA graph): step j takes the j-th token of every
+            # request that has one; the others write to a spare row.
+            slots = b.state_slot.long()
+            first, end = b.cu_q[:-1].long(), b.cu_q[1:].long()
+            s = state[slots]
+            s_all = torch.empty((T + 1, self.n), dtype=torch.float32, device=u.device)
+            for j in range(b.max_q_len):
+                idx = first + j
+                live = (idx < end)[:, None]
+                idx = torch.where(idx < end, idx, torch.full_like(idx, T))
+                s = torch.where(live, self.decay * s + u[idx.clamp(max=T - 1)], s)
+                s_all[idx] = s
+            state[slots] = s
+            ops.linear_add(s_all[:T].to(ctx.rt.dtype), self.w_out, resid)
 
     @dataclass
     class ToyConfig:
@@ -125,7 +132,8 @@ def test_toy_mixer_with_state(tmp_path):
     cfg = ToyConfig(hidden_size=40, vocab_size=97, num_hidden_layers=4, state_size=24, decay=0.9, intermediate_size=56)
     folder = write_random_model(cfg, 7, str(tmp_path / "toy"))
     eng = Engine.from_pretrained(folder, dtype="float32", page_size=16, num_pages=24, max_requests=4)
-    assert len(eng.cache.state) == 2 and len(eng.cache.k) == 2 and not eng.use_graphs
+    assert len(eng.cache.state) == 2 and len(eng.cache.k) == 2
+    assert eng.use_graphs          # per-request state does not rule out replayed decode steps
     g = torch.Generator().manual_seed(3)
     reqs = {f"t{i}": torch.randint(0, 97, (n,), generator=g).tolist() for i, n in enumerate([45, 9, 70, 30, 18])}
     ref = {rid: plain_toy(folder, toks) for rid, toks in reqs.items()}
@@ -136,10 +144,24 @@ def test_toy_mixer_with_state(tmp_path):
         for (rid, p), row in got.items():
             assert float((row.double() - ref[rid][p]).abs().max()) < 1e-4, (rid, p)
     # a slot's state starts from zero for the next request that takes it
-    outs = eng.generate([reqs["t1"], reqs["t3"]], max_new_tokens=5)
-    assert outs == [eng.generate(reqs["t1"], max_new_tokens=5), eng.generate(reqs["t3"], max_new_tokens=5)]
+    outs = eng.generate([reqs["t1"], reqs["t3"]], max_new_tokens=12)
+    assert outs == [eng.generate(reqs["t1"], max_new_tokens=12), eng.generate(reqs["t3"], max_new_tokens=12)]
+    assert len(eng._graphs) > 0    # the decode steps were replayed from graphs: each ran once, or the state would be off
     for p, o in zip((reqs["t1"], reqs["t3"]), outs):
-        assert int(torch.argmax(plain_toy(folder, p)[-1])) == o[0]
+        ref_logits = plain_toy(folder, p + o[:-1])
+        for i, tok in enumerate(o):
+            row = ref_logits[len(p) - 1 + i]
+            top2 = torch.topk(row, 2).values
+            if float(top2[0] - top2[1]) > 1e-3:
+                assert int(torch.argmax(row)) == tok, i
+    # a part that says it synchronises with the host keeps its model's steps out of graphs
+    eng.model.blocks[1].mixer.__class__.graph_safe = False
+    try:
+        eng2 = Engine.from_pretrained(folder, dtype="float32", page_size=16, num_pages=24, max_requests=4)
+        assert not eng2.use_graphs
+        assert eng2.generate(reqs["t1"], max_new_tokens=12) == outs[0] and len(eng2._graphs) == 0
+    finally:
+        eng.model.blocks[1].mixer.__class__.graph_safe = True
 
 
 def define_routed_toy():
@@ -292,3 +314,251 @@ def test_toy_routing_and_position_encodings(tmp_path):
             assert float((row.double() - logits[p]).abs().max()) < 1e-4, (rid, p)
             compared += 1
     assert compared > 0.9 * 4 * sum(map(len, reqs.values()))
+
+
+def define_latent_toy():
+    """A mixer that caches ONE latent vector per token (and pays for one tensor), a feed-forward that routes
+    with sigmoid scores, a selection bias and a scale factor through the package's router kernel, a norm that is
+    not an RMS norm, and rotary pairs of neighbouring dims: all registered from outside the package."""
+    from dlm_b200.parts.base import CacheTensor, FeedForward, Mixer, Norm, PagedCache, ParamSpec, PartSpec
+    from dlm_b200.parts.model import ModelSpec
+    from dlm_b200.registry import register_architecture, register_part
+
+    class ToyLatentAttention(Mixer):
+        """c_t = W_c h_t is all that is cached for token t (one vector of `latent` numbers; it serves as key
+        and as value of a single kv head); q heads attend over the cached latents; a window is optional."""
+
+        def __init__(self, hidden_size, num_heads, latent, window=None, page_size=None):
+            self.hidden, self.nh, self.d, self.window, self.page_size = hidden_size, num_heads, latent, window, page_size
+
+        def param_specs(self):
+            return [ParamSpec("q.weight", (self.nh * self.d, self.hidden)), ParamSpec("c.weight", (self.d, self.hidden)),
+                    ParamSpec("o.weight", (self.hidden, self.nh * self.d))]
+
+        def load(self, tensors, rt):
+            self.wq, self.wc, self.wo = (rt.matrix(tensors[n + ".weight"]) for n in "qco")
+
+        def cache_need(self):
+            return PagedCache((CacheTensor("latent", 1, self.d),), self.window, self.page_size)
+
+        def forward(self, h, resid, ctx, call):
+            ops, b, rt = ctx.rt.ops, ctx.batch, ctx.rt
+            view = ctx.paged(call)
+            lat = view.tensors["latent"]                               # [pages + 1, 1, page, d]
+            c = ops.linear(h, self.wc, None, rt.dtype)
+            lat.view(-1, self.d)[view.group.slots.long()] = c          # one head: slot = page * page_size + offset
+            q = ops.linear(h, self.wq, None, rt.dtype)
+            o = ops.attention(q, lat, lat, view.group.block_table, b.cu_q, b.kv_len, self.window or 0,
+                              self.d ** -0.5, self.nh, 1, self.d, b.max_q_len, b.max_kv_len, b.num_single)
+            ops.linear_add(o, self.wo, resid)
+
+    class ToySigmoidRoutedExperts(FeedForward):
+        """k experts by sigmoid score plus a per-expert selection bias; weights are the scores of the chosen,
+        renormalised and scaled: every option of the package's router kernel that softmax routing leaves unused.
+        The router reads the 32-bit normalised residual whatever the norm before it is."""
+
+        def __init__(self, hidden_size, num_experts, top_k, expert_size, scale):
+            self.hidden, self.E, self.k, self.I, self.scale = hidden_size, num_experts, top_k, expert_size, scale
+
+        def param_specs(self):
+            return [ParamSpec("router", (self.E, self.hidden)), ParamSpec("router_bias", (self.E,), init="bias"),
+                    ParamSpec("gate_up", (self.E, 2 * self.I, self.hidden)), ParamSpec("down", (self.E, self.hidden, self.I))]
+
+        def load(self, tensors, rt):
+            self.router, self.gate_up, self.down = (rt.matrix(tensors[n]).contiguous() for n in ("router", "gate_up", "down"))
+            self.bias = rt.vector(tensors["router_bias"])
+
+        def forward(self, h, resid, ctx, pre_norm=None):
+            ops = ctx.rt.ops
+            x32 = pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)
+            ids, wts, _ = ops.router_topk(x32, self.router, self.E, self.k, True, False, score="sigmoid",
+                                          scale=self.scale, select_bias=self.bias)
+            offsets, rows, dest = ops.moe_permute(ids, self.E)
+            act = ops.grouped_swiglu(h, self.gate_up, offsets, rows)
+            ops.moe_combine(ops.grouped_linear(act, self.down, offsets), dest, wts, None, None, resid)
+
+    class ToyCenteredNorm(Norm):
+        """(x - mean) / sqrt(var + eps) * weight: not an RMS norm, so no kernel can fuse it."""
+
+        def __init__(self, size, eps):
+            self.size, self.eps = size, eps
+
+        def param_specs(self):
+            return [ParamSpec("weight", (self.size,), init="norm")]
+
+        def load(self, tensors, rt):
+            self.weight = rt.vector(tensors["weight"])
+
+        def forward(self, x, rt, rows=None, out_dtype=None):
+            if rows is not None:
+                x = x[rows.long()]
+            mu = x.mean(-1, keepdim=True)
+            var = ((x - mu) ** 2).mean(-1, keepdim=True)
+            return (((x - mu) / torch.sqrt(var + self.eps)) * self.weight).to(out_dtype or rt.dtype)
+
+    @dataclass
+    class LatentToyConfig:
+        hidden_size: int
+        vocab_size: int
+        num_hidden_layers: int
+        latent: int
+        num_experts: int
+        expert_size: int
+        window: int
+        eps: float = 1e-5
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(**{k: raw[k] for k in cls.__dataclass_fields__ if k in raw})
+
+        def to_dict(self):
+            d = dict(self.__dict__)
+            d["architectures"] = ["ToyLatentLM"]
+            return d
+
+    def build_spec(cfg):
+        norm = PartSpec("toy_centered_norm", {"size": cfg.hidden_size, "eps": cfg.eps})
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            if i % 3 == 2:
+                # the package's attention with rotary pairs of neighbouring dims and the package's softmax experts
+                # behind the toy norm
+                mixer = PartSpec("gqa_attention", {"hidden_size": cfg.hidden_size, "num_heads": 2, "num_kv_heads": 2,
+                                                   "head_dim": 16, "qkv_bias": False, "window": None,
+                                                   "position": PartSpec("rope_interleaved", {"head_dim": 16, "theta": 300.0,
+                                                                                             "rotary_dim": 8})})
+                ffn = PartSpec("moe_softmax_topk", {"hidden_size": cfg.hidden_size, "num_experts": cfg.num_experts,
+                                                    "top_k": 2, "expert_intermediate_size": cfg.expert_size,
+                                                    "norm_topk_prob": True, "shared_intermediate_size": None})
+            else:
+                # latents in pages of their own size; every other such layer is windowed: three groups in all
+                mixer = PartSpec("toy_latent_attention", {"hidden_size": cfg.hidden_size, "num_heads": 3, "latent": cfg.latent,
+                                                          "window": cfg.window if i % 3 == 1 else None, "page_size": 32})
+                ffn = PartSpec("toy_sigmoid_routed", {"hidden_size": cfg.hidden_size, "num_experts": cfg.num_experts,
+                                                      "top_k": 2, "expert_size": cfg.expert_size, "scale": 1.5})
+            layers.append(PartSpec("prenorm", {"norm1": norm, "mixer": mixer, "norm2": norm, "ffn": ffn}))
+        n = cfg.num_hidden_layers
+        return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
+                         layer_prefixes=[f"toy.layers.{i}." for i in range(n)], final_norm=norm,
+                         final_norm_prefix="toy.norm.", embed_name="toy.embed.weight", lm_head_name="toy.head.weight")
+
+    register_part("mixer", "toy_latent_attention", ToyLatentAttention)
+    register_part("ffn", "toy_sigmoid_routed", ToySigmoidRoutedExperts)
+    register_part("norm", "toy_centered_norm", ToyCenteredNorm)
+    register_architecture("ToyLatentLM", LatentToyConfig, build_spec)
+    return LatentToyConfig
+
+
+def plain_latent_toy(folder, tokens):
+    """The latent toy over a whole sequence in plain PyTorch (double precision), and per position the smallest
+    gap of any routing decision (in score units)."""
+    import plain_qwen2_moe as plain
+    cfg, t = plain.load_folder(folder)
+    t = {k: v.double() for k, v in t.items()}
+    T, H, d, E = len(tokens), cfg["hidden_size"], cfg["latent"], cfg["num_experts"]
+    pos = torch.arange(T)
+    x = t["toy.embed.weight"][torch.tensor(tokens)]
+    gap = torch.full((T,), float("inf"), dtype=torch.float64)
+
+    def cnorm(v, w):
+        mu = v.mean(-1, keepdim=True)
+        var = ((v - mu) ** 2).mean(-1, keepdim=True)
+        return (v - mu) / torch.sqrt(var + cfg["eps"]) * w
+
+    def experts(n2, ids, wts, gate_up, down):
+        out = torch.zeros_like(n2)
+        for j in range(T):
+            for e, w in zip(ids[j].tolist(), wts[j]):
+                out[j] += w * plain.swiglu_ffn(n2[j:j + 1], gate_up[e][0::2], gate_up[e][1::2], down[e], lambda z: z)[0]
+        return out
+
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"toy.layers.{i}."
+        n = cnorm(x, t[p + "norm1.weight"])
+        if i % 3 == 2:
+            q, k, v = (n @ t[p + f"mixer.{c}_proj.weight"].T for c in "qkv")
+            inv = torch.tensor([300.0 ** (-2.0 * j / 8) for j in range(4)], dtype=torch.float64).to(torch.float32)
+
+            def pairs(u):          # [T, heads, 16]: dims (0,1), (2,3), (4,5), (6,7) rotate, the rest pass
+                ang = (pos.to(torch.float32)[:, None] * inv[None, :]).double()
+                sin, cos = torch.sin(ang)[:, None, :], torch.cos(ang)[:, None, :]
+                a, b = u[..., 0:8:2], u[..., 1:8:2]
+                out = u.clone()
+                out[..., 0:8:2] = a * cos - b * sin
+                out[..., 1:8:2] = a * sin + b * cos
+                return out
+            ctx = plain.attention(pairs(q.view(T, 2, 16)), pairs(k.view(T, 2, 16)), v.view(T, 2, 16), None).reshape(T, 32)
+            x = x + ctx @ t[p + "mixer.o_proj.weight"].T
+            n2 = cnorm(x, t[p + "norm2.weight"])
+            logits = n2 @ t[p + "ffn.gate.weight"].T
+            sp = torch.sort(plain.softmax(logits), dim=-1, descending=True).values
+            gap = torch.minimum(gap, sp[:, 1] - sp[:, 2])
+            ids, wts = plain.route_topk(logits, 2, True)
+            gu = torch.stack([torch.stack([t[f"{p}ffn.experts.{e}.gate_proj.weight"], t[f"{p}ffn.experts.{e}.up_proj.weight"]], 1)
+                              .reshape(-1, H) for e in range(E)])
+            dn = torch.stack([t[f"{p}ffn.experts.{e}.down_proj.weight"] for e in range(E)])
+            x = x + experts(n2, ids, wts, gu, dn)
+        else:
+            c = (n @ t[p + "mixer.c.weight"].T).view(T, 1, d)
+            q = (n @ t[p + "mixer.q.weight"].T).view(T, 3, d)
+            ctx = plain.attention(q, c, c, cfg["window"] if i % 3 == 1 else None).reshape(T, 3 * d)
+            x = x + ctx @ t[p + "mixer.o.weight"].T
+            n2 = cnorm(x, t[p + "norm2.weight"])
+            score = 1.0 / (1.0 + torch.exp(-(n2 @ t[p + "ffn.router"].T)))
+            pick = score + t[p + "ffn.router_bias"][None, :]
+            order = torch.sort(pick, dim=-1, descending=True, stable=True)
+            gap = torch.minimum(gap, order.values[:, 1] - order.values[:, 2])
+            ids = order.indices[:, :2]
+            w = torch.gather(score, 1, ids)
+            w = w / w.sum(-1, keepdim=True) * 1.5
+            x = x + experts(n2, ids, w, t[p + "ffn.gate_up"], t[p + "ffn.down"])
+    return cnorm(x, t["toy.norm.weight"]) @ t["toy.head.weight"].T, gap
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_latent_cache_sigmoid_router_and_other_norm(tmp_path, dtype):
+    import cuttings
+    from dlm_b200.engine import Engine
+    from dlm_b200.weights import write_random_model
+    LatentToyConfig = define_latent_toy()
+    cfg = LatentToyConfig(hidden_size=48, vocab_size=131, num_hidden_layers=6, latent=32, num_experts=6, expert_size=24,
+                          window=20)
+    folder = write_random_model(cfg, 13, str(tmp_path / "latent"))
+    eng = Engine.from_pretrained(folder, dtype=dtype, page_size=16, num_pages=32, max_requests=4)
+    # three groups: latents kept whole and latents windowed (pages of 32), keys and values (the engine's pages of 16)
+    assert sorted(zip(eng.cache.group_windows, eng.cache.group_page_size)) == [(0, 16), (0, 32), (20, 32)]
+    # a latent layer holds one tensor of 32 numbers a token, an attention layer two of 2 x 16
+    width = 2 if dtype == "bfloat16" else 4
+    assert eng.cache.bytes_per_token() == (4 * 32 + 2 * 2 * 2 * 16) * width
+    assert eng.use_graphs
+    g = torch.Generator().manual_seed(8)
+    reqs = {f"t{i}": torch.randint(0, 131, (n,), generator=g).tolist() for i, n in enumerate([50, 7, 90, 33])}
+    ref = {rid: plain_latent_toy(folder, toks) for rid, toks in reqs.items()}
+    tol, margin = (1e-4, 1e-5) if dtype == "float32" else (2e-2, 2e-3)
+    mixed, _ = cuttings.mixed(reqs, max_live=3, seed=6)
+    compared = total = 0
+    for steps in (cuttings.whole(reqs), cuttings.portions(reqs), cuttings.tail_decode(reqs, 10), mixed):
+        got = cuttings.run_trace(eng, steps)
+        assert len(got) == sum(map(len, reqs.values()))
+        for (rid, p), row in got.items():
+            logits, gap = ref[rid]
+            total += 1
+            if float(gap[p]) < margin:
+                continue
+            assert float((row.double() - logits[p]).abs().max()) < tol, (rid, p)
+            compared += 1
+    print(f"compared {compared} of {total}")
+    assert compared > (0.9 if dtype == "float32" else 0.5) * total
+    for st in eng.cache.stats():
+        assert st.used_pages == 0
+    # greedy generation runs its decode steps from graphs
+    p = reqs["t3"]
+    out = eng.generate(p, max_new_tokens=10)
+    assert len(eng._graphs) > 0
+    if dtype == "float32":
+        logits, gap = plain_latent_toy(folder, p + out[:-1])
+        for i, tok in enumerate(out):
+            row = logits[len(p) - 1 + i]
+            top2 = torch.topk(row, 2).values
+            if float(top2[0] - top2[1]) > 1e-3 and float(gap[:len(p) + i].min()) > margin:
+                assert int(torch.argmax(row)) == tok, i
