@@ -1,8 +1,12 @@
 """Serving benchmark: decode tokens per second of the Qwen1.5-MoE-A2.7B-sized model with
-random weights (bfloat16) on one B200, plus prefill, roofline and end-to-end figures.
+random weights (bfloat16) on one B200, plus prefill, roofline and end-to-end figures; in the same
+line, the same measurements at the layer sizes of Qwen2-57B-A14B (`sizes_57b`) and a
+continuous-batching workload on the windowed variant of the model (`serving`).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --workload serving      # continuous batching on the windowed model, a line of its own
+    python bench.py --no-extras             # the headline model only
+    python bench.py --workload serving      # the continuous-batching workload alone, a line of its own
+    python bench.py --sizes 57b             # the larger model alone as the headline
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -28,6 +32,7 @@ MODEL = dict(
     num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408, shared_expert_intermediate_size=5632,
     norm_topk_prob=False, decoder_sparse_step=1, intermediate_size=5632, vocab_size=151936, rope_theta=1000000.0,
     rms_norm_eps=1e-6, use_sliding_window=False, tie_word_embeddings=False, max_position_embeddings=4096)
+MODEL_A = dict(MODEL)
 FULL_LAYERS = MODEL["num_hidden_layers"]
 MODEL_NAME = "Qwen1.5-MoE-A2.7B"
 # The larger model of the same family (--sizes 57b; about 114 GB of weights with all 28 layers).
@@ -99,13 +104,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def weight_bytes_per_decode_step(cfg, batch, layers, esz=2):
-    """Bytes a decode step has to read: every weight it uses once.  Routed experts: the
-    expected number of distinct experts a batch of `batch` tokens touches per layer."""
+def weight_bytes_per_decode_step(cfg, batch, layers, esz=2, distinct=None):
+    """Bytes a decode step has to read: every weight it uses once.  Routed experts: `distinct` experts
+    with rows per layer (the mean over the layers of what the step's own routing gave); without it, the
+    expected number of distinct experts a batch of `batch` tokens touches."""
     H, Q, KV = cfg.hidden_size, cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
     E, k, I, Is = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
     attn = ((Q + 2 * KV) * H + H * Q) * esz
-    distinct = E * (1.0 - (1.0 - k / E) ** batch)
+    if distinct is None:
+        distinct = E * (1.0 - (1.0 - k / E) ** batch)
     moe = (E + 1) * H * esz + distinct * 3 * I * H * esz + 3 * Is * H * esz
     head = cfg.vocab_size * H * esz
     return layers * (attn + moe) + head
@@ -126,7 +133,7 @@ def run_reference():
     return 0
 
 
-def run_serving(args) -> int:
+def run_serving(args) -> dict:
     """Continuous batching on the windowed variant of the model: 64 requests, prompt lengths uniform in
     [256, 16384], output lengths uniform in [64, 512], seeded uniform token ids; a request arrives every
     second step, so portions of prompts (2,048-token portions) run beside decoded tokens in the same step.
@@ -136,7 +143,7 @@ def run_serving(args) -> int:
     from dlm_b200.config import Qwen2MoeConfig
     from dlm_b200.engine import Engine
 
-    raw = dict(MODEL)
+    raw = dict(MODEL_A)
     raw.update(num_hidden_layers=args.layers, use_sliding_window=True, sliding_window=4096,
                max_window_layers=min(21, max(args.layers - 3, 0)), max_position_embeddings=32768)
     cfg = Qwen2MoeConfig.from_dict(raw)
@@ -177,86 +184,76 @@ def run_serving(args) -> int:
         "seconds": round(t1 - t0, 3), "generated_tokens": produced, "prompt_tokens": sum(plen),
         "prompt_tok_s": round(sum(plen) / (t1 - t0), 1), "steps": steps, "complete": ok,
         "config": {"model": "Qwen1.5-MoE-A2.7B sizes, window", "requests": n_req, "layers": args.layers,
-                   "layers_full": FULL_LAYERS, "pool_tokens": pool_tokens, "portion": 2048, "page_size": 64,
+                   "layers_full": MODEL_A["num_hidden_layers"], "pool_tokens": pool_tokens, "portion": 2048, "page_size": 64,
                    "arrivals": "one request every second step"},
         "scheduler": {k: st[k] for k in ("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished")},
         "pages": st["pages"], "clocks": clocks,
     }
-    print(json.dumps(line))
-    return 0 if ok else 1
+    del eng
+    return line
 
 
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (reported)")
-    ap.add_argument("--sizes", default="a2.7b", choices=["a2.7b", "57b"],
-                    help="57b: the layer sizes of Qwen2-57B-A14B instead (not the default line)")
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
-    ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
-                    help="serving: the continuous-batching workload on the windowed model, instead of the default line")
-    args = ap.parse_args()
-    global FULL_LAYERS, MODEL_NAME
-    if args.sizes == "57b":
-        MODEL.update(SIZES_57B)
-        FULL_LAYERS, MODEL_NAME = SIZES_57B["num_hidden_layers"], "Qwen2-57B-A14B"
-    if args.layers is None:
-        args.layers = FULL_LAYERS
-    if args.impl == "reference":
-        return run_reference()
-    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
-        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
-        return 2
-    if args.workload == "serving":
-        return run_serving(args)
-    args.warmup = max(args.warmup, 3)
+class Measurement:
+    """One model on the device and the measurements taken on it: decode steps at several batch sizes
+    (device time of the replayed step, and end to end through run_step) and one 2,048-token prefill."""
 
-    import torch
+    def __init__(self, raw, layers, prompt_len, context, max_batch, pk):
+        import torch
 
-    from dlm_b200.config import Qwen2MoeConfig
-    from dlm_b200.engine import Engine
+        from dlm_b200.config import Qwen2MoeConfig
+        from dlm_b200.engine import Engine
+        self.torch = torch
+        raw = dict(raw)
+        raw["num_hidden_layers"] = layers
+        self.cfg = Qwen2MoeConfig.from_dict(raw)
+        self.layers, self.prompt_len, self.pk = layers, prompt_len, pk
+        torch.cuda.set_device(0)
+        self.page = 64
+        pool_tokens = max_batch * (prompt_len + 256) + 4096
+        t_load = time.time()
+        self.eng = Engine.from_random(self.cfg, seed=0, dtype="bfloat16", page_size=self.page, max_tokens=pool_tokens,
+                                      max_requests=max_batch, max_step_tokens=2048, max_context=context)
+        torch.cuda.synchronize()
+        self.load_s = time.time() - t_load
+        self.gen = torch.Generator().manual_seed(0)
+        # the routing of every captured step: the permutation's offsets stay in the graph's memory
+        self.offsets = []
+        ops = self.eng.rt.ops
+        permute = ops.moe_permute
 
-    pk = peaks()
-    raw = dict(MODEL)
-    raw["num_hidden_layers"] = args.layers
-    cfg = Qwen2MoeConfig.from_dict(raw)
-    torch.cuda.set_device(0)
-    max_batch = 64 if not args.no_points else args.batch
-    page = 64
-    pool_tokens = max_batch * (args.prompt_len + 256) + 4096
-    t_load = time.time()
-    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", page_size=page, max_tokens=pool_tokens,
-                             max_requests=max_batch, max_step_tokens=2048, max_context=args.context)
-    torch.cuda.synchronize()
-    load_s = time.time() - t_load
-    V = cfg.vocab_size
-    gen = torch.Generator().manual_seed(0)
-    counter = eng.rt.ops
+        def recording_permute(ids, E):
+            out = permute(ids, E)
+            self.offsets.append(out[0])
+            return out
+        ops.moe_permute = recording_permute
 
-    def prompts(n, length):
-        return [torch.randint(0, V, (length,), generator=gen).tolist() for _ in range(n)]
+    def close(self):
+        import gc
+        self.eng._graphs.clear()
+        self.eng = None
+        self.offsets = []
+        gc.collect()
+        self.torch.cuda.empty_cache()
 
-    def decode_run(batch, steps, warmup, sample_clocks=False):
+    def prompts(self, n, length):
+        return [self.torch.randint(0, self.cfg.vocab_size, (length,), generator=self.gen).tolist() for _ in range(n)]
+
+    def decode(self, batch, steps, warmup, sample_clocks=False):
         """Prefills `batch` prompts through the scheduler, then times `steps` decode steps of the step
         function (device time) and the same number through run_step (end to end)."""
-        ids = [eng.submit(p, max_new_tokens=10 ** 6) for p in prompts(batch, args.prompt_len)]
+        torch, eng = self.torch, self.eng
+        ids = [eng.submit(p, max_new_tokens=10 ** 6) for p in self.prompts(batch, self.prompt_len)]
         started = set()
         while len(started) < batch:                   # admit and prefill everything
             started.update(rid for rid, _ in eng.run_step())
         # every request now decodes one token per step
-        for _ in range(warmup):
+        self.offsets = []
+        for _ in range(max(warmup, 3)):
             eng.run_step()
         torch.cuda.synchronize()
         # device time of the decode step itself: `steps` replays of the captured step (the step function
         # and the arg-max over its logits, all kernels of one decode step), no host work in between
-        key = next(k for k in eng._graphs if k[0] == batch and k[1] >= args.prompt_len)
+        key = next(k for k in eng._graphs if k[0] == batch and k[1] >= self.prompt_len)
         ent = eng._graphs[key]
         sampler = ClockSampler()
         if sample_clocks:
@@ -272,12 +269,17 @@ def main() -> int:
         torch.cuda.synchronize()
         t1 = time.time()
         dev_ms = e0.elapsed_time(e1)
-        launches = ent["launches"] * steps
         clocks = None
         if sample_clocks:
             time.sleep(0.2)
             sampler.stop()
             clocks = sampler.summary(t0, t1)
+        # the experts that had rows in the replayed step, per layer (the last capture's offsets)
+        distinct = None
+        sparse = sum(1 for i in range(self.layers) if self.cfg.layer_is_sparse(i))
+        if sparse and len(self.offsets) >= sparse:
+            offs = torch.stack(self.offsets[-sparse:]).cpu()
+            distinct = float(((offs[:, 1:] - offs[:, :-1]) > 0).sum(dim=1).double().mean())
         # end to end: wall clock around the public loop, host tokens in and out every step
         torch.cuda.synchronize()
         w0 = time.perf_counter()
@@ -286,70 +288,25 @@ def main() -> int:
             produced += len(eng.run_step())
         torch.cuda.synchronize()
         w1 = time.perf_counter()
-        ctx = eng.cache.manager.length(0) if eng.cache.manager.is_open(0) else args.prompt_len
+        ctx = eng.cache.manager.length(0) if eng.cache.manager.is_open(0) else self.prompt_len
         for i in ids:
             eng.abort(i)
         eng.scheduler.drain_finished()
-        return dict(dev_ms=dev_ms, e2e_s=w1 - w0, produced=produced, launches=launches, clocks=clocks, ctx=ctx)
+        ms = dev_ms / steps
+        kv_bytes = batch * (self.prompt_len + max(warmup, 3) + 2 + steps // 2) * eng.cache.bytes_per_token()
+        step_bytes = weight_bytes_per_decode_step(self.cfg, batch, self.layers, distinct=distinct) + kv_bytes
+        achieved = step_bytes / (ms / 1e3) / 1e9
+        return dict(ms=ms, tok_s=batch * steps / (dev_ms / 1e3), e2e_tok_s=produced / (w1 - w0),
+                    launches=ent["launches"] * steps, clocks=clocks, ctx=ctx, distinct=distinct,
+                    step_bytes=step_bytes, achieved=achieved, frac=achieved / self.pk["hbm_gbs"],
+                    h2d=int(eng.cache.last_h2d_bytes))
 
-    if args.only_prefill:
-        T = 2048
+    def prefill(self, T=2048, repeats=4):
+        torch, eng = self.torch, self.eng
         times = []
-        for it in range(3):
+        for _ in range(repeats):
             s = eng.cache.open()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            eng.step([(s, prompts(1, T)[0], [T - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
-            eng.cache.close(s)
-        print(json.dumps({"prefill_ms": [round(t, 3) for t in times], "tokens": T, "layers": args.layers}))
-        return 0
-    main_run = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
-    ms_per_step = main_run["dev_ms"] / args.steps
-    value = args.batch * args.steps / (main_run["dev_ms"] / 1e3)
-    e2e_value = main_run["produced"] / main_run["e2e_s"]
-    kv_bytes = args.batch * (args.prompt_len + args.warmup + args.steps // 2) * eng.cache.bytes_per_token()
-    step_bytes = weight_bytes_per_decode_step(cfg, args.batch, args.layers) + kv_bytes
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
-
-    out = {
-        "metric": "decode tok/s @ batch %d (%s sizes, bf16, random weights)" % (args.batch, MODEL_NAME),
-        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
-        "impl": "ours",
-        "config": {
-            "model": MODEL_NAME + " sizes", "global_batch": args.batch, "seq_len": args.context,
-            "parallelism": "1 GPU", "prompt_len": args.prompt_len, "layers": args.layers, "layers_full": FULL_LAYERS,
-            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-            "head_dim": cfg.head_dim, "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
-            "moe_inter": cfg.moe_intermediate_size, "shared_inter": cfg.shared_expert_intermediate_size,
-            "vocab": cfg.vocab_size, "page_size": page,
-            "l2": "inputs larger than L2: a step reads %.1f GB" % (step_bytes / 1e9),
-            "timed": "K replays of the captured decode step (CUDA graph), CUDA events",
-            "peaks": pk["source"]},
-        "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s",
-                "h2d_bytes_per_step": int(eng.cache.last_h2d_bytes), "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": int(main_run["launches"]),
-        "clocks": main_run["clocks"],
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "load_s": round(load_s, 1),
-    }
-    if not args.no_points:
-        pts = {}
-        for b in (1, 64):
-            r = decode_run(b, max(8, args.steps // 2), 3)
-            pts[f"decode_b{b}"] = round(b * max(8, args.steps // 2) / (r["dev_ms"] / 1e3), 2)
-        out["points"] = pts
-        # prefill of one 2,048-token prompt as one step
-        T = 2048
-        times = []
-        for it in range(4):
-            s = eng.cache.open()
-            toks = prompts(1, T)[0]
+            toks = self.prompts(1, T)[0]
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -358,11 +315,152 @@ def main() -> int:
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
             eng.cache.close(s)
-        pms = min(times[1:])
-        flops = prefill_flops(cfg, T, args.layers)
-        out["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
-                          "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-    eng.rt.ops.check_errors()
+        pms = min(times[1:]) if len(times) > 1 else times[0]
+        flops = prefill_flops(self.cfg, T, self.layers)
+        return {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                "frac": round(flops / (pms / 1e3) / (self.pk["bf16_tflops"] * 1e12), 4),
+                "peak_tflops": self.pk["bf16_tflops"], "all_ms": [round(t, 3) for t in times]}
+
+
+def layers_that_fit(raw, want, reserve_gb=40.0):
+    """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
+    the cache pool, the head, graphs and activations."""
+    import torch
+    H, I, Is, E = raw["hidden_size"], raw["moe_intermediate_size"], raw["shared_expert_intermediate_size"], raw["num_experts"]
+    Q = raw["num_attention_heads"] * raw["head_dim"]
+    KV = raw["num_key_value_heads"] * raw["head_dim"]
+    per_layer = 2 * ((Q + 2 * KV) * H + H * Q + (E + 1) * H + E * 3 * I * H + 3 * Is * H)
+    free, _ = torch.cuda.mem_get_info(0)
+    fit = int((free - reserve_gb * 1e9) // per_layer)
+    return max(1, min(want, fit))
+
+
+def measure_57b(args, pk) -> dict:
+    """The layer sizes of Qwen2-57B-A14B: decode at batch 1 / 8 / 64 (context 2,048) and a 2,048-token
+    prefill, each with its fraction of the measured peak."""
+    raw = dict(MODEL_A)
+    raw.update(SIZES_57B)
+    raw["max_position_embeddings"] = 4096
+    full = SIZES_57B["num_hidden_layers"]
+    layers = layers_that_fit(raw, full if args.layers_57b is None else args.layers_57b)
+    m = Measurement(raw, layers, 2048, 4096, 64, pk)
+    out = {"model": "Qwen2-57B-A14B sizes", "layers": layers, "layers_full": full, "prompt_len": 2048,
+           "load_s": round(m.load_s, 1)}
+    for b in (8, 1, 64):
+        r = m.decode(b, max(4, args.steps // 4), 3, sample_clocks=(b == 8))
+        out[f"decode_b{b}"] = round(r["tok_s"], 2)
+        out[f"decode_b{b}_ms"] = round(r["ms"], 4)
+        out[f"decode_b{b}_frac"] = round(r["frac"], 4)
+        out[f"decode_b{b}_experts"] = r["distinct"]
+        if b == 8:
+            out["clocks"] = r["clocks"]
+    out["prefill"] = m.prefill(2048, repeats=3)
+    m.eng.rt.ops.check_errors()
+    m.close()
+    return out
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (reported)")
+    ap.add_argument("--layers-57b", type=int, default=None, help="layers of the larger model in `sizes_57b` (default: all "
+                    "28 if they fit)")
+    ap.add_argument("--sizes", default="a2.7b", choices=["a2.7b", "57b"],
+                    help="57b: the layer sizes of Qwen2-57B-A14B as the headline (no extras)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
+    ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
+    ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="serving: the continuous-batching workload on the windowed model, instead of the default line")
+    args = ap.parse_args()
+    global FULL_LAYERS, MODEL_NAME
+    if args.sizes == "57b":
+        MODEL.update(SIZES_57B)
+        FULL_LAYERS, MODEL_NAME = SIZES_57B["num_hidden_layers"], "Qwen2-57B-A14B"
+        args.no_extras = True
+    if args.impl == "reference":
+        return run_reference()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.workload == "serving":
+        if args.layers is None:
+            args.layers = MODEL_A["num_hidden_layers"]
+        line = run_serving(args)
+        print(json.dumps(line))
+        return 0 if line["complete"] else 1
+    if args.layers is None:
+        args.layers = FULL_LAYERS
+    args.warmup = max(args.warmup, 3)
+    pk = peaks()
+    max_batch = 64 if not args.no_points else args.batch
+    m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk)
+    cfg = m.cfg
+    if args.only_prefill:
+        pre = m.prefill(2048, repeats=3)
+        print(json.dumps({"prefill_ms": pre["all_ms"], "tokens": 2048, "layers": args.layers}))
+        return 0
+    main_run = m.decode(args.batch, args.steps, args.warmup, sample_clocks=True)
+    out = {
+        "metric": "decode tok/s @ batch %d (%s sizes, bf16, random weights)" % (args.batch, MODEL_NAME),
+        "value": round(main_run["tok_s"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)", "impl": "ours",
+        "config": {
+            "model": MODEL_NAME + " sizes", "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "1 GPU", "prompt_len": args.prompt_len, "layers": args.layers, "layers_full": FULL_LAYERS,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "experts": cfg.num_experts, "top_k": cfg.num_experts_per_tok,
+            "moe_inter": cfg.moe_intermediate_size, "shared_inter": cfg.shared_expert_intermediate_size,
+            "vocab": cfg.vocab_size, "page_size": m.page,
+            "l2": "inputs larger than L2: a step reads %.1f GB" % (main_run["step_bytes"] / 1e9),
+            "timed": "K replays of the captured decode step (CUDA graph), CUDA events",
+            "peaks": pk["source"]},
+        "e2e": {"value": round(main_run["e2e_tok_s"], 2), "unit": "tokens/s",
+                "h2d_bytes_per_step": main_run["h2d"], "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(main_run["launches"]),
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": round(main_run["achieved"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main_run["frac"], 4), "experts_with_rows": main_run["distinct"]},
+        "load_s": round(m.load_s, 1),
+    }
+    if not args.no_points:
+        pts, fracs = {}, {f"decode_b{args.batch}": round(main_run["frac"], 4)}
+        for b in (1, 64):
+            r = m.decode(b, max(8, args.steps // 2), 3)
+            pts[f"decode_b{b}"] = round(r["tok_s"], 2)
+            fracs[f"decode_b{b}"] = round(r["frac"], 4)
+        out["points"] = pts
+        out["points_frac"] = fracs          # of the HBM peak, bytes from the experts each step really used
+        out["prefill"] = m.prefill(2048, repeats=4)
+        out["prefill"].pop("all_ms")
+    m.eng.rt.ops.check_errors()
+    m.close()
+    if not args.no_extras and not args.no_points:
+        sv_args = argparse.Namespace(layers=MODEL_A["num_hidden_layers"])
+        sv = run_serving(sv_args)
+        out["serving"] = {"generated_tok_s": sv["value"], "prompt_tok_s": sv["prompt_tok_s"], "seconds": sv["seconds"],
+                          "steps": sv["steps"], "mean_step_ms": round(1e3 * sv["seconds"] / max(sv["steps"], 1), 3),
+                          "requests": sv["config"]["requests"], "layers": sv["config"]["layers"],
+                          "prompt_tokens": sv["prompt_tokens"], "generated_tokens": sv["generated_tokens"],
+                          "preemptions": sv["scheduler"]["preemptions"],
+                          "high_water_pages": [p["high_water"] for p in sv["pages"]],
+                          "pool_pages": [p["total"] for p in sv["pages"]], "complete": sv["complete"],
+                          "clocks": sv["clocks"]}
+        import gc
+
+        import torch
+        gc.collect()
+        torch.cuda.empty_cache()
+        out["sizes_57b"] = measure_57b(args, pk)
     print(json.dumps(out))
     return 0
 
