@@ -68,6 +68,13 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
                  float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
                  int score_fn, float scale, const float* select_bias, cudaStream_t stream);
 
+// router_topk followed by moe_permute (below), in one launch when the step has few tokens (T <= 16; measured: beyond that
+// the one block that chooses for every token is slower than the separate kernels).
+void router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
+                         float* wts, float* gate, int32_t* offsets, int32_t* rows, int32_t* dest, int T, int H, int E,
+                         int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,
+                         const float* select_bias, cudaStream_t stream);
+
 // Groups the n = T * k (token, choice) pairs by expert: offsets[E + 1], rows[n] = token of each sorted row,
 // dest[n] = sorted row of pair (t, j).
 void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int32_t* rows, int32_t* dest,

@@ -323,8 +323,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t full_bar[NST], empty_bar[NST];
     __shared__ int s_abort;
-    dep_wait();
-    dep_launch_next();
     const uint32_t raw_addr = smem_u32(smem_dyn);
     unsigned char* smem_raw = smem_dyn + (((raw_addr + 1023u) & ~1023u) - raw_addr);     // the tiles want 1024-byte alignment
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw + NST * STAGE_BYTES);  // [ROWS][PITCH]
@@ -332,7 +330,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int r = blockIdx.x;
     const int kvh = blockIdx.y / p.head_passes, pass = blockIdx.y % p.head_passes;
     const int sp = blockIdx.z;
-    if (p.cu_q[r + 1] - p.cu_q[r] != 1) return;
+    if (p.cu_q[r + 1] - p.cu_q[r] != 1) {      // (the step's lengths and tables were there before the step began)
+        dep_wait();
+        return;
+    }
     const int group = p.nh / p.nkv;
     const int h0 = kvh * group + pass * ROWS;
     const int n_heads = min(ROWS, group - pass * ROWS);
@@ -353,6 +354,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // The kernel before this one wrote the step's new key and value (position len - 1) and the queries.
+    // Everything older in the cache, the block table and the lengths were there before the step began, so the
+    // producer asks for every tile that does not hold position len - 1 before it waits for that kernel;
+    // everybody else waits first.
+    const int tiles_before_wait = (t_begin + n_tiles * BKV > pos) ? max(n_tiles - 1, 0) : n_tiles;
+    if (warp != WARPS) {
+        dep_wait();
+        dep_launch_next();
+    }
 
     float o[DT][4];
 #pragma unroll
@@ -366,8 +376,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         if (lane == 0) {
             const int32_t* table = p.block_table + (long long)r * p.table_width;
             const int rows_total = p.total_pages * p.nkv * p.page_size;
+            bool waited = false;
             for (int it = 0; it < n_tiles; ++it) {
                 const int s = it % NST;
+                // (a stage is given back only after the consumers, who have waited, have read it)
+                if (it >= tiles_before_wait && !waited) { dep_wait(); waited = true; }
                 if (it >= NST && !mbar_wait(&empty_bar[s], ((it / NST) & 1) ^ 1, abort_flag)) break;
                 const int key0 = t_begin + it * BKV;
                 const int lp = key0 >> p.page_shift;
@@ -383,6 +396,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 }
             }
         }
+        dep_wait();        // every thread has waited for the kernel before this one when the block ends
     } else if (n_tiles > 0) {
         // ----------------------------------------------------------------- consumers
         for (int idx = tid; idx < ROWS * CPR; idx += WARPS * 32) {

@@ -168,24 +168,20 @@ router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __
     }
 }
 
-// Scores from the logits (score_fn 0: softmax over the experts; 1: a sigmoid of each logit), the k best
-// (ties: lower index; with select_bias the choice is made on score + bias, the weight stays the score),
-// optional renormalisation of the chosen weights, a constant factor, and the shared expert's sigmoid gate.
-// One warp per token.
-__global__ void __launch_bounds__(128)
-router_select_kernel(const float* logits, int32_t* ids, float* wts,
-                     float* gate, int T, int E, int k, int norm, int has_gate, int score_fn, float scale,
-                     const float* __restrict__ select_bias) {
-    extern __shared__ float smem[];
-    dep_wait();
-    dep_launch_next();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
+// One token's choice, by one warp: scores from the logits (score_fn 0: softmax over the experts; 1: a sigmoid
+// of each logit), the k best (ties: lower index; with select_bias the choice is made on score + bias, the
+// weight stays the score), optional renormalisation of the chosen weights, a constant factor, and the shared
+// expert's sigmoid gate.  `prob`: 2 * (E + 1) floats of shared memory of this warp's own.
+template <bool COHERENT>
+__device__ __forceinline__ void select_token(float* prob, const float* logits, int32_t* ids, float* wts, float* gate,
+                                             int t, int E, int k, int norm, int has_gate, int score_fn, float scale,
+                                             const float* __restrict__ select_bias) {
+    const int lane = threadIdx.x & 31;
     const int rows = E + (has_gate ? 1 : 0);
-    float* prob = smem + warp * 2 * (E + 1);     // the scores
     float* pick = prob + (E + 1);                // what the choice is made on (score, or score + bias)
-    for (int e = lane; e < rows; e += 32) prob[e] = logits[(long long)t * rows + e];
+    // COHERENT: the logits were written by other blocks of this launch; read them where those writes are
+    for (int e = lane; e < rows; e += 32)
+        prob[e] = COHERENT ? __ldcg(logits + (long long)t * rows + e) : logits[(long long)t * rows + e];
     __syncwarp();
     if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-prob[E]));
     if (score_fn == 0) {
@@ -238,14 +234,25 @@ router_select_kernel(const float* logits, int32_t* ids, float* wts,
     }
 }
 
-constexpr int PERMUTE_THREADS = 1024;
-
-__global__ void __launch_bounds__(PERMUTE_THREADS)
-moe_permute_kernel(const int32_t* ids, int n, int k, int E, int32_t* offsets,
-                   int32_t* rows, int32_t* dest, int* err) {
-    extern __shared__ int sm[];
+// One warp per token.
+__global__ void __launch_bounds__(128)
+router_select_kernel(const float* logits, int32_t* ids, float* wts,
+                     float* gate, int T, int E, int k, int norm, int has_gate, int score_fn, float scale,
+                     const float* __restrict__ select_bias) {
+    extern __shared__ float smem[];
     dep_wait();
     dep_launch_next();
+    const int warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    select_token<false>(smem + warp * 2 * (E + 1), logits, ids, wts, gate, t, E, k, norm, has_gate, score_fn, scale,
+                        select_bias);
+}
+
+// Groups n (token, choice) pairs by expert with the threads of one block: counts, an exclusive scan, and the
+// rows.  `sm`: 2 * E ints of shared memory.  Every thread of the block calls it.
+__device__ __forceinline__ void permute_block(int* sm, const int32_t* ids, int n, int k, int E, int32_t* offsets,
+                                              int32_t* rows, int32_t* dest, int* err) {
     int* count = sm;          // [E]
     int* cursor = sm + E;     // [E]
     const int tid = threadIdx.x;
@@ -277,6 +284,91 @@ moe_permute_kernel(const int32_t* ids, int n, int k, int E, int32_t* offsets,
             dest[i] = 0;
         }
     }
+}
+
+constexpr int PERMUTE_THREADS = 1024;
+
+__global__ void __launch_bounds__(PERMUTE_THREADS)
+moe_permute_kernel(const int32_t* ids, int n, int k, int E, int32_t* offsets,
+                   int32_t* rows, int32_t* dest, int* err) {
+    extern __shared__ int sm[];
+    dep_wait();
+    dep_launch_next();
+    permute_block(sm, ids, n, k, E, offsets, rows, dest, err);
+}
+
+// Few tokens (a decode step of at most 16): logits, choice and grouping in ONE launch.  Blocks compute logits as
+// router_logits_kernel does (blockIdx.x = token, blockIdx.y = a block of experts, the same sums in the same
+// order); the block that finishes last (a counter in global memory, put back to zero by that block, so
+// launches of this kernel must not overlap) then chooses for every token and groups the pairs by expert.
+__device__ unsigned int g_router_blocks_done;
+
+template <typename TX, typename T, bool VEC>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
+                    float* logits, int32_t* ids, float* wts, float* gate, int32_t* offsets, int32_t* rows_out,
+                    int32_t* dest, int T_, int H, int E, int k, int norm, int has_gate, int score_fn, float scale,
+                    const float* __restrict__ select_bias, int* err) {
+    extern __shared__ float smem[];
+    __shared__ float scratch[32];
+    __shared__ int s_last;
+    dep_wait();
+    dep_launch_next();
+    const int rows = E + (has_gate ? 1 : 0);
+    float* x = smem;            // [H]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float ss = 0.f;
+    for (int i = tid; i < H; i += blockDim.x) {
+        const float v = to_f32(h[(long long)t * H + i]);
+        x[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (norm_w != nullptr) {
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+        for (int i = tid; i < H; i += blockDim.x) x[i] = (x[i] * inv) * norm_w[i];
+    }
+    __syncthreads();
+    const int e = blockIdx.y * ROUTER_WARPS + warp;
+    if (e < rows) {
+        const T* wr = w + (long long)e * H;
+        float s = 0.f;
+        if (VEC) {
+#pragma unroll 4
+            for (int b = 0; b < H; b += 256) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int i = b + 128 * half + lane * 4;
+                    if (i < H) {
+                        float wv[4];
+                        load4(wr + i, wv);
+                        const float4 xa = *reinterpret_cast<const float4*>(x + i);
+                        s = fmaf(xa.x, wv[0], s); s = fmaf(xa.y, wv[1], s); s = fmaf(xa.z, wv[2], s); s = fmaf(xa.w, wv[3], s);
+                    }
+                }
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
+        }
+        s = warp_sum(s);
+        if (lane == 0) __stcg(logits + (long long)t * rows + e, s);
+    }
+    // the last block to get here does the rest
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned total = gridDim.x * gridDim.y;
+        s_last = atomicAdd(&g_router_blocks_done, 1u) == total - 1 ? 1 : 0;
+        if (s_last) g_router_blocks_done = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int tt = warp; tt < T_; tt += ROUTER_WARPS)
+        select_token<true>(smem + warp * 2 * (E + 1), logits, ids, wts, gate, tt, E, k, norm, has_gate, score_fn,
+                           scale, select_bias);
+    __syncthreads();
+    permute_block(reinterpret_cast<int*>(smem), ids, T_ * k, k, E, offsets, rows_out, dest, err);
 }
 
 }  // namespace
@@ -340,6 +432,41 @@ void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int3
     launch_dep(moe_permute_kernel, 1, PERMUTE_THREADS, sizeof(int) * 2 * E, stream, ids, n < 0 ? 0 : n, k, E, offsets,
                rows, dest, error_flag_ptr());
     check_launch("moe_permute");
+}
+
+void router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
+                         float* wts, float* gate, int32_t* offsets, int32_t* rows_out, int32_t* dest, int T, int H,
+                         int E, int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,
+                         const float* select_bias, cudaStream_t stream) {
+    if (T <= 0) return;
+    const int rows = E + (has_gate ? 1 : 0);
+    const size_t need = sizeof(float) * (size_t)H;
+    const size_t need2 = sizeof(float) * (size_t)ROUTER_WARPS * 2 * (E + 1);
+    const size_t smem = need > need2 ? need : need2;
+    if (T > 16 || smem > 200 * 1024 || E > 4096) {
+        router_topk(h, w, norm_w, eps, logits, ids, wts, gate, T, H, E, k, norm, has_gate, dtype, h_is_f32, score_fn,
+                    scale, select_bias, stream);
+        moe_permute(ids, T * k, k, E, offsets, rows_out, dest, stream);
+        return;
+    }
+    DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
+    DLM_CHECK(score_fn == 0 || score_fn == 1, "router: score function must be 0 (softmax) or 1 (sigmoid)");
+    const bool x32 = norm_w != nullptr || h_is_f32 != 0;
+    const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    dim3 grid(T, (rows + ROUTER_WARPS - 1) / ROUTER_WARPS);
+#define DLM_ROUTER_FUSED(TX, TW, VEC)                                                                         \
+    {                                                                                                         \
+        auto kern = router_fused_kernel<TX, TW, VEC>;                                                         \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
+        launch_dep(kern, grid, ROUTER_THREADS, smem, stream, static_cast<const TX*>(h),                       \
+                   static_cast<const TW*>(w), norm_w, eps, logits, ids, wts, gate, offsets, rows_out, dest, T, H, E, \
+                   k, norm, has_gate, score_fn, scale, select_bias, error_flag_ptr());                        \
+    }
+    if (dtype == F32) { if (vec) DLM_ROUTER_FUSED(float, float, true) else DLM_ROUTER_FUSED(float, float, false) }
+    else if (x32) { if (vec) DLM_ROUTER_FUSED(float, __nv_bfloat16, true) else DLM_ROUTER_FUSED(float, __nv_bfloat16, false) }
+    else { if (vec) DLM_ROUTER_FUSED(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER_FUSED(__nv_bfloat16, __nv_bfloat16, false) }
+#undef DLM_ROUTER_FUSED
+    check_launch("router_fused");
 }
 
 }  // namespace dlmk

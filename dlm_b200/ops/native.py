@@ -226,6 +226,29 @@ class NativeOps:
                            _p(select_bias), self._stream())
         return ids, wts, gate
 
+    def route(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
+              select_bias=None):
+        """``router_topk`` and ``moe_permute`` together: ``(ids, wts, gate, offsets, rows, dest)``.  A step
+        of at most 16 tokens does all of it in one launch."""
+        T, H = h.shape
+        assert w.shape == (E + (1 if has_gate else 0), H)
+        assert h.dtype in (w.dtype, torch.float32) and (norm_weight is None or h.dtype == torch.float32)
+        score_fn = {"softmax": 0, "sigmoid": 1}[score]
+        h_is_f32 = int(norm_weight is None and h.dtype == torch.float32 and w.dtype != torch.float32)
+        dev = h.device
+        ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+        wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+        gate = torch.empty((T,), dtype=torch.float32, device=dev) if has_gate else None
+        logits = torch.empty((T, w.shape[0]), dtype=torch.float32, device=dev)
+        offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+        rows = torch.empty((T * k,), dtype=torch.int32, device=dev)
+        dest = torch.empty((T, k), dtype=torch.int32, device=dev)
+        self.launches += 1 if T <= 16 else 3
+        self.k.router_topk_permute(_p(h), _p(w), _p(norm_weight), float(eps), _p(logits), _p(ids), _p(wts), _p(gate),
+                                   _p(offsets), _p(rows), _p(dest), T, H, E, k, int(norm), int(has_gate),
+                                   _dt(w.dtype), h_is_f32, score_fn, float(scale), _p(select_bias), self._stream())
+        return ids, wts, gate, offsets, rows, dest
+
     def moe_permute(self, ids, E):
         T, k = ids.shape
         n = T * k

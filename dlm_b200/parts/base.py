@@ -154,6 +154,7 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+
     def forward(self, h: torch.Tensor, resid: torch.Tensor, ctx: "StepContext", pre_norm: "Norm | None" = None) -> None:
         """``pre_norm`` is the norm that produced ``h`` from ``resid``; a part that needs the
         normalised input in 32-bit (a router) may apply it again to the residual itself."""

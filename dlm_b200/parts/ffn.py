@@ -97,6 +97,7 @@ class SoftmaxTopKMoE(FeedForward):
 
     def forward(self, h, resid, ctx: StepContext, pre_norm=None):
         ops = ctx.rt.ops
+        rms = pre_norm.fusable_rms() if pre_norm is not None else None
         shared = None
         branch = ops.branch(h.shape[0])
         if self.Is:
@@ -106,14 +107,12 @@ class SoftmaxTopKMoE(FeedForward):
                 shared = ops.linear(sact, self.ws_down, None, torch.float32)
         # router logits (and the shared expert's gate) from the 32-bit normalised residual: an RMS norm is
         # applied again inside the router's kernel, any other norm is asked for a 32-bit result
-        rms = pre_norm.fusable_rms() if pre_norm is not None else None
         if rms is not None:
-            ids, wts, gate = ops.router_topk(resid, self.w_router, self.E, self.k, self.norm, self.has_gate,
-                                             norm_weight=rms[0], eps=rms[1])
+            ids, wts, gate, offsets, rows, dest = ops.route(resid, self.w_router, self.E, self.k, self.norm,
+                                                            self.has_gate, norm_weight=rms[0], eps=rms[1])
         else:
             x = h if pre_norm is None else pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)
-            ids, wts, gate = ops.router_topk(x, self.w_router, self.E, self.k, self.norm, self.has_gate)
-        offsets, rows, dest = ops.moe_permute(ids, self.E)
+            ids, wts, gate, offsets, rows, dest = ops.route(x, self.w_router, self.E, self.k, self.norm, self.has_gate)
         act = ops.grouped_swiglu(h, self.w_gate_up, offsets, rows)
         y = ops.grouped_linear(act, self.w_down, offsets)
         branch.join()

@@ -160,6 +160,10 @@ class PlainOps:
             wts = torch.where(s > 0, wts / s, wts)
         return ids.to(torch.int32), wts * scale, gate
 
+    def route(self, h, w, E, k, norm, has_gate, **kw):
+        ids, wts, gate = self.router_topk(h, w, E, k, norm, has_gate, **kw)
+        return (ids, wts, gate) + tuple(self.moe_permute(ids, E))
+
     def moe_permute(self, ids, E):
         T, k = ids.shape
         flat = ids.reshape(-1).long()

@@ -192,6 +192,30 @@ def test_router_score_functions(ops, ref, dtype, E, k, H, norm, score, scale, bi
         assert not torch.equal(plain[0], want[0])
 
 
+@pytest.mark.parametrize("T", [1, 8, 37, 64, 65, 700])
+@pytest.mark.parametrize("E,k,H,gate", [(60, 4, 2048, True), (12, 3, 256, False), (64, 8, 3584, True), (5, 1, 72, False)])
+def test_route_in_one_launch_equals_the_separate_kernels(ops, T, E, k, H, gate):
+    """Logits, choice and grouping together (one launch up to 64 tokens) give what the separate kernels give,
+    bit for bit, also when called again and again (the launch counts its blocks in a global counter)."""
+    x = rand((T, H), torch.float32, 27, 2.0)
+    nw = 1 + rand((H,), torch.float32, 28, 0.1)
+    w = rand((E + int(gate), H), torch.bfloat16, 29, 0.3)
+    ids, wts, g = ops.router_topk(x, w, E, k, True, gate, norm_weight=nw, eps=1e-6)
+    off, rows, dest = ops.moe_permute(ids, E)
+    for _ in range(3):
+        i2, w2, g2, off2, rows2, dest2 = ops.route(x, w, E, k, True, gate, norm_weight=nw, eps=1e-6)
+        assert torch.equal(ids, i2) and torch.equal(wts, w2) and torch.equal(off, off2)
+        if gate:
+            assert torch.equal(g, g2)
+        o = off2.tolist()
+        for e in range(E):
+            assert sorted(rows2[o[e]:o[e + 1]].tolist()) == sorted(rows[o[e]:o[e + 1]].tolist())
+        flat = dest2.reshape(-1).long()
+        assert sorted(flat.tolist()) == list(range(T * k))
+        assert torch.equal(rows2[flat].long(), torch.arange(T * k, device="cuda") // k)
+    ops.check_errors()
+
+
 def test_router_hand_values_and_ties(ops):
     # src/forward/cpu.rs:1580-1595: logits [1, 2, 0], top-2 -> experts [1, 0]; renormalised weights sum to 1
     h = torch.eye(3, device="cuda")[:1]                     # picks column 0 of w^T

@@ -119,13 +119,14 @@ def test_dense_ffn_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T", [37, 9, 1])       # 9 and 1: routing in one launch
 @pytest.mark.parametrize("E,k,norm,Is,gate", [(6, 2, True, 40, True), (10, 3, False, None, False), (7, 1, True, 24, False)])
-def test_moe_part(dtype, E, k, norm, Is, gate):
+def test_moe_part(dtype, E, k, norm, Is, gate, T):
     from dlm_b200.parts.ffn import SoftmaxTopKMoE
     from dlm_b200.parts.norm import RMSNorm
     torch.manual_seed(E)
     rt = runtime(dtype)
-    H, I, T = 72, 24, 37
+    H, I = 72, 24
     part = SoftmaxTopKMoE(H, E, k, I, norm, shared_intermediate_size=Is, shared_gate=gate)
     t = {"gate.weight": 0.5 * torch.randn(E, H)}
     for e in range(E):
