@@ -101,6 +101,9 @@ template <typename TOut, bool VEC, bool WIDE>
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut* out,
                                const int32_t* rows, int n_rows, int H, float eps) {
     __shared__ float s_part[8];
+    // the norm's weight is no kernel's output: ask for it before waiting for the kernel before this one
+    for (int off = threadIdx.x * 128; off < H * (int)sizeof(float); off += blockDim.x * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(w) + off));
     dep_wait();
     dep_launch_next();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -19,6 +19,17 @@ __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
 }
 
+// Asks for a row of the router's matrix to be brought into L2 (one 128-byte line a lane and round).  The matrix
+// is never written by a kernel, so this may run before dep_wait(): the row is then near when the dot product
+// starts.
+template <typename T>
+__device__ __forceinline__ void prefetch_row_l2(const T* row, int H, int lane) {
+    const char* base = reinterpret_cast<const char*>(row);
+    const int bytes = H * (int)sizeof(T);
+    for (int off = lane * 128; off < bytes; off += 32 * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+}
+
 // Router logits: blockIdx.x = token, blockIdx.y = a block of ROUTER_WARPS experts, one warp per
 // expert.  Each logit is one warp's dot product summed in a fixed order (lane l takes elements
 // 4l..4l+3 and 128+4l..128+4l+3 of every 256, so that a quarter warp reads 128 consecutive bytes of the
@@ -34,6 +45,10 @@ router_logits_kernel(const TX* h, const T* __restrict__ w, const float* __restri
                      float* logits, int H, int rows) {
     extern __shared__ float smem[];
     __shared__ float scratch[32];
+    {
+        const int e_mine = blockIdx.y * ROUTER_WARPS + (threadIdx.x >> 5);
+        if (e_mine < rows) prefetch_row_l2(w + (long long)e_mine * H, H, threadIdx.x & 31);
+    }
     dep_wait();
     dep_launch_next();
     float* x = smem;            // [H]
@@ -312,9 +327,13 @@ router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restric
     extern __shared__ float smem[];
     __shared__ float scratch[32];
     __shared__ int s_last;
+    const int rows = E + (has_gate ? 1 : 0);
+    {
+        const int e_mine = blockIdx.y * ROUTER_WARPS + (threadIdx.x >> 5);
+        if (e_mine < rows) prefetch_row_l2(w + (long long)e_mine * H, H, threadIdx.x & 31);
+    }
     dep_wait();
     dep_launch_next();
-    const int rows = E + (has_gate ? 1 : 0);
     float* x = smem;            // [H]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float ss = 0.f;
