@@ -162,15 +162,33 @@ def run_serving(args) -> dict:
     sampler.start()
     t0 = time.time()
     submitted, produced, steps = 0, 0, 0
+    # per step: device time between two events around it, wall time, and whether it carried prompt tokens
+    records, prompt_seen = [], eng.scheduler.stats().prompt_tokens
     while submitted < n_req or eng.scheduler.has_work():
         if submitted < n_req and steps % 2 == 0:
             eng.submit(prompts[submitted], max_new_tokens=olen[submitted])
             submitted += 1
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        e0.record()
         out = eng.run_step()
+        e1.record()
+        e1.synchronize()
+        w1 = time.perf_counter()
+        now = eng.scheduler.stats().prompt_tokens
+        records.append((e0, e1, w1 - w0, now - prompt_seen, len(out)))
+        prompt_seen = now
         produced += len(out)
         steps += 1
     torch.cuda.synchronize()
     t1 = time.time()
+    kinds = {"decode_only": [], "with_prompt_le_256": [], "with_prompt_gt_256": []}
+    for e0, e1, wall, ptoks, rows in records:
+        kind = "decode_only" if ptoks == 0 else ("with_prompt_le_256" if ptoks <= 256 else "with_prompt_gt_256")
+        kinds[kind].append((e0.elapsed_time(e1), 1e3 * wall))
+    step_kinds = {k: {"steps": len(v), "device_ms_mean": round(sum(a for a, _ in v) / len(v), 3),
+                      "wall_ms_mean": round(sum(b for _, b in v) / len(v), 3)} for k, v in kinds.items() if v}
+    device_s = sum(e0.elapsed_time(e1) for e0, e1, *_ in records) / 1e3
     time.sleep(0.2)
     sampler.stop()
     clocks = sampler.summary(t0, t1)
@@ -188,6 +206,8 @@ def run_serving(args) -> dict:
                    "arrivals": "one request every second step"},
         "scheduler": {k: st[k] for k in ("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished")},
         "pages": st["pages"], "clocks": clocks,
+        # how much of the wall time the device was at work (events around every step), and the steps by kind
+        "device_busy_frac": round(device_s / (t1 - t0), 4), "step_kinds": step_kinds,
     }
     del eng
     return line
@@ -322,6 +342,46 @@ class Measurement:
                 "peak_tflops": self.pk["bf16_tflops"], "all_ms": [round(t, 3) for t in times]}
 
 
+def run_sweep(args, pk) -> dict:
+    """Further contexts: decode steps at batch 1 / 8 / 64 with 1k to 32k tokens of context each (as far as the
+    pool holds them), and prompts of 8k and 16k tokens prefilled in portions of 2,048, each with its fraction of
+    the measured peak."""
+    out = {"metric": "sweep over contexts (%s sizes, bf16, random weights)" % MODEL_NAME, "layers": args.layers,
+           "layers_full": FULL_LAYERS, "decode": {}, "prefill": {}}
+    for ctx in (1024, 4096, 8192, 16384, 32768):
+        for b in (1, 8, 64):
+            if b * ctx > 600_000:          # 64 x 16k and 64 x 32k would not fit beside the weights
+                continue
+            m = Measurement(MODEL, args.layers, ctx, ctx + 512, b, pk)
+            r = m.decode(b, 8, 3)
+            out["decode"][f"b{b}_ctx{ctx}"] = {"tok_s": round(r["tok_s"], 1), "ms": round(r["ms"], 3),
+                                                "frac": round(r["frac"], 4)}
+            m.close()
+    import torch
+    for plen in (8192, 16384):
+        m = Measurement(MODEL, args.layers, plen, plen + 512, 1, pk)
+        eng, times = m.eng, []
+        for _ in range(2):
+            s = eng.cache.open()
+            toks = m.prompts(1, plen)[0]
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(0, plen, 2048):
+                eng.step([(s, toks[i:i + 2048], [2047] if i + 2048 >= plen else [])])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            eng.cache.close(s)
+        ms = min(times)
+        flops = prefill_flops(m.cfg, plen, args.layers)
+        out["prefill"][f"prompt{plen}"] = {"tok_s": round(plen / (ms / 1e3), 1), "ms": round(ms, 2),
+                                           "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        m.eng.rt.ops.check_errors()
+        m.close()
+    return out
+
+
 def layers_that_fit(raw, want, reserve_gb=40.0):
     """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
     the cache pool, the head, graphs and activations."""
@@ -377,8 +437,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
-                    help="serving: the continuous-batching workload on the windowed model, instead of the default line")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep"],
+                    help="serving: the continuous-batching workload on the windowed model, instead of the default line; "
+                         "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own")
     args = ap.parse_args()
     global FULL_LAYERS, MODEL_NAME
     if args.sizes == "57b":
@@ -400,6 +461,9 @@ def main() -> int:
         args.layers = FULL_LAYERS
     args.warmup = max(args.warmup, 3)
     pk = peaks()
+    if args.workload == "sweep":
+        print(json.dumps(run_sweep(args, pk)))
+        return 0
     max_batch = 64 if not args.no_points else args.batch
     m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk)
     cfg = m.cfg
@@ -454,6 +518,7 @@ def main() -> int:
                           "preemptions": sv["scheduler"]["preemptions"],
                           "high_water_pages": [p["high_water"] for p in sv["pages"]],
                           "pool_pages": [p["total"] for p in sv["pages"]], "complete": sv["complete"],
+                          "device_busy_frac": sv["device_busy_frac"], "step_kinds": sv["step_kinds"],
                           "clocks": sv["clocks"]}
         import gc
 

@@ -3,9 +3,11 @@
 //
 // One persistent block per multiprocessor walks a contiguous range of work items; an item is a tile
 // of 16 rows of W (of one expert), so that a block reads one long contiguous stretch of memory.
-// A producer warp brings the tile into shared memory, one bulk copy (cp.async.bulk, completion on an
-// mbarrier) per row and up to 4 KB each, three stages deep; rows longer than 2,048 elements come in
-// chunks.  Eight consumer warps split a chunk along K; each multiplies its slice by the rows of A,
+// A producer warp brings the tile into shared memory with bulk copies (cp.async.bulk, completion on an
+// mbarrier), three stages deep: the whole tile in ONE copy when its rows lie back to back in memory and fit
+// a stage and are shorter than 2,048 elements, else one copy per row and chunk of 2,048 elements.  (Issuing a
+// bulk copy costs about 60 ns whatever its size; with one copy per row a tile could not take less than a
+// microsecond, which held products with rows shorter than 1,500 elements below the memory's bandwidth.)  Eight consumer warps split a chunk along K; each multiplies its slice by the rows of A,
 // which it holds in registers, in tensor-core MMAs with the roles swapped (16 rows of W are the MMA's
 // M, 8 rows of A its N; mma.sync m16n8k16, bfloat16 in, 32-bit accumulation), and the eight partial
 // sums of a tile are added in a fixed order through shared memory, one tile late, so that no warp
@@ -13,9 +15,13 @@
 //
 // K is walked in blocks of 32.  Lane (g = lane / 4, t = lane % 4) takes the 8 consecutive elements
 // 8t..8t+7 of rows g and g + 8 of the weight tile and of row g of A; the two MMAs of a block take
-// elements {0,1 | 2,3} and {4,5 | 6,7} of those as their k-slices.  A sum does not care in which
-// order its terms are listed, and A and W list them alike.  Rows of a stage are 64 bytes (mod 128)
-// apart, so that the 16-byte reads of a quarter warp fall into distinct banks.
+// elements {0,1 | 2,3} and {4,5 | 6,7} of those as their k-slices.  Even and odd blocks add into two
+// accumulators (two chains of dependent MMAs instead of one; a warp's MMAs, not the memory, were what a tile
+// of short rows waited for), which are added at the end.  A sum does not care in which
+// order its terms are listed, and A and W list them alike.  Rows copied one by one lie 64 bytes (mod 128)
+// apart in a stage, so that the 16-byte reads of a quarter warp fall into distinct banks; a tile copied whole
+// keeps its rows back to back, and its reads meet two to a bank when the row length is a multiple of 64
+// elements, which the consumers, idle most of the time, can afford.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out sets a block-wide flag, all roles
 // leave their loops, the producer waits (bounded again) for its copies in flight, and the kernel
@@ -55,6 +61,7 @@ struct StreamParams {
     int n_chunks, kc;     // chunks of K per tile, elements per chunk (the last may be shorter)
     int slice;            // elements of a chunk per consumer warp: a multiple of 32, at most 256
     int pitch;            // bytes between the rows of a stage
+    int whole_tile;       // a tile's rows are contiguous in memory and come as one copy
     int* err;
 };
 
@@ -63,11 +70,14 @@ __device__ __forceinline__ void bulk_copy(void* smem_dst, const void* src, uint3
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ uint4 lds128(const void* p) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
-    return v;
+// The MMA without `volatile`: the compiler may interleave the two accumulator chains and move the loads of
+// the next blocks of K between them (the mbarrier operations around a stage clobber memory, so nothing
+// crosses them).
+__device__ __forceinline__ void mma_free(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 struct Work { int expert, row0, m_count, tile; };
@@ -147,6 +157,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                 if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 const int k0 = c * p.kc;
                 const uint32_t len = (uint32_t)min(p.kc, p.K - k0);
+                if (p.whole_tile) {
+                    // the rows that exist (the last tile of a matrix may be short; what lies behind them in the
+                    // stage is left over from earlier tiles and only meets outputs that are not stored)
+                    if (lane == 0) {
+                        const uint32_t bytes = (uint32_t)min(RT, p.N - wk.tile * RT) * (uint32_t)p.K * 2u;
+                        mbar_expect_tx(&full_bar[s], bytes);
+                        bulk_copy(smem + s * stage_bytes,
+                                  p.w + (long long)wk.expert * p.w_expert_stride + (long long)wk.tile * RT * p.ldw, bytes,
+                                  &full_bar[s]);
+                    }
+                    continue;
+                }
                 if (lane == 0) mbar_expect_tx(&full_bar[s], RT * len * 2);
                 __syncwarp();
                 if (lane < RT) bulk_copy(smem + s * stage_bytes + (size_t)lane * p.pitch, src_row + k0, len * 2, &full_bar[s]);
@@ -215,11 +237,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
             const int passes = (wk.m_count + MP - 1) / MP;
             for (int pass = 0; pass < passes && ok; ++pass) {
                 const int m0 = pass * MP;
-                float acc[NT][4];
+                float acc[NT][2][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+                    for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.f;
                 for (int c = 0; c < p.n_chunks; ++c, ++it) {
                     const int k0 = c * p.kc;
                     const int len = min(p.kc, p.K - k0);
@@ -246,19 +268,32 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                     const uint32_t s = it % STAGES;
                     if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
                     const unsigned char* st = smem + s * stage_bytes + (size_t)(kw + 8 * t) * 2;
+                    // the weights of GB blocks of K are read before their MMAs are issued
+                    constexpr int GB = NT >= 4 ? 2 : 4;
 #pragma unroll
-                    for (int b = 0; b < 8; ++b) {
-                        if (b < nb) {
-                            // K is a multiple of 8: a lane's 8 elements are all in or all out
-                            uint4 w0 = make_uint4(0, 0, 0, 0), w1 = make_uint4(0, 0, 0, 0);
-                            if (kw + 32 * b + 8 * t < len) {
-                                w0 = lds128(st + (size_t)g * p.pitch + 64 * b);
-                                w1 = lds128(st + (size_t)(g + 8) * p.pitch + 64 * b);
+                    for (int b0 = 0; b0 < 8; b0 += GB) {
+                        if (b0 < nb) {
+                            uint4 wa[GB], wb[GB];
+#pragma unroll
+                            for (int j = 0; j < GB; ++j) {
+                                const int b = b0 + j;
+                                wa[j] = wb[j] = make_uint4(0, 0, 0, 0);
+                                // K is a multiple of 8: a lane's 8 elements are all in or all out
+                                if (b < nb && kw + 32 * b + 8 * t < len) {
+                                    wa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * p.pitch + 64 * b);
+                                    wb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * p.pitch + 64 * b);
+                                }
                             }
 #pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) {
-                                mma_bf16(acc[nt], w0.x, w1.x, w0.y, w1.y, xb[nt][b].x, xb[nt][b].y);
-                                mma_bf16(acc[nt], w0.z, w1.z, w0.w, w1.w, xb[nt][b].z, xb[nt][b].w);
+                            for (int j = 0; j < GB; ++j) {
+                                const int b = b0 + j;
+                                if (b < nb) {
+#pragma unroll
+                                    for (int nt = 0; nt < NT; ++nt) {
+                                        mma_free(acc[nt][0], wa[j].x, wb[j].x, wa[j].y, wb[j].y, xb[nt][b].x, xb[nt][b].y);
+                                        mma_free(acc[nt][1], wa[j].z, wb[j].z, wa[j].w, wb[j].w, xb[nt][b].z, xb[nt][b].w);
+                                    }
+                                }
                             }
                         }
                     }
@@ -275,10 +310,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                 float* mine = red + ((size_t)(ep & 1) * CW + warp) * 16 * (MP + 1);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    mine[g * (MP + 1) + nt * 8 + 2 * t] = acc[nt][0];
-                    mine[g * (MP + 1) + nt * 8 + 2 * t + 1] = acc[nt][1];
-                    mine[(g + 8) * (MP + 1) + nt * 8 + 2 * t] = acc[nt][2];
-                    mine[(g + 8) * (MP + 1) + nt * 8 + 2 * t + 1] = acc[nt][3];
+                    mine[g * (MP + 1) + nt * 8 + 2 * t] = acc[nt][0][0] + acc[nt][1][0];
+                    mine[g * (MP + 1) + nt * 8 + 2 * t + 1] = acc[nt][0][1] + acc[nt][1][1];
+                    mine[(g + 8) * (MP + 1) + nt * 8 + 2 * t] = acc[nt][0][2] + acc[nt][1][2];
+                    mine[(g + 8) * (MP + 1) + nt * 8 + 2 * t + 1] = acc[nt][0][3] + acc[nt][1][3];
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_full[ep & 1]);
@@ -353,9 +388,13 @@ void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, i
     p.kc = ((K + p.n_chunks - 1) / p.n_chunks + 31) / 32 * 32;
     if (p.kc > K) p.kc = K;
     p.slice = ((p.kc + CW - 1) / CW + 31) / 32 * 32;
-    // rows of a stage 64 bytes (mod 128) apart
+    // rows of a stage 64 bytes (mod 128) apart; or, a tile in one copy, back to back as they lie in memory
     const int row_bytes = p.kc * 2;
-    p.pitch = row_bytes + ((64 - row_bytes % 128) + 128) % 128;
+    // (measured on rows of 512 / 1,024 / 1,408 / 1,536 / 2,048 elements: one copy per tile 3.1 / 5.7 / 6.2 / 6.2 /
+    // 6.2 TB/s, one copy per row 2.3 / 4.5 / 5.7 / 6.1 / 6.3: the row copies' padding keeps the reads free of
+    // bank conflicts, which shows once the rows are long enough for their issue not to matter)
+    p.whole_tile = (p.n_chunks == 1 && ldw == K && K < 2048) ? 1 : 0;
+    p.pitch = p.whole_tile ? row_bytes : row_bytes + ((64 - row_bytes % 128) + 128) % 128;
     p.err = error_flag_ptr();
     const int groups = expert_offsets ? (num_experts < M ? num_experts : M) : 1;
     const long long items = (long long)p.tiles * groups;
