@@ -7,6 +7,8 @@ continuous-batching workload on the windowed variant of the model (`serving`).
     python bench.py --no-extras             # the headline model only
     python bench.py --workload serving      # the continuous-batching workload alone, a line of its own
     python bench.py --sizes 57b             # the larger model alone as the headline
+    python bench.py --workload sweep        # decode at 1k-32k tokens of context, prompts of 8k and 16k
+    python bench.py --workload kernels      # the weight-streaming product alone, by shape and row length
 
 A step is one decode step of the whole batch.  One JSON line is printed.
 """
@@ -382,6 +384,77 @@ def run_sweep(args, pk) -> dict:
     return out
 
 
+def run_kernels(pk) -> dict:
+    """The weight-streaming product alone, timed with CUDA events inside a captured graph, the weights rotated
+    over several copies so that L2 does not hold them: the decode step's shapes (8 rows), the routed experts'
+    products at 1 / 8 / 64 tokens, and 8 rows against 256 MB of weights with rows of 512 to 4,096 elements."""
+    import torch
+
+    from dlm_b200.ops import native_ops
+    ops = native_ops(fast=True)
+    dev = "cuda"
+    bf = torch.bfloat16
+
+    def timed(fn, copies, reps=3):
+        for c in range(copies):
+            fn(c)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                for c in range(copies):
+                    fn(c)
+        g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1000 / (5 * reps * copies)
+
+    out = {"metric": "weight-streaming product alone: us and TB/s", "peak_gbs": pk["hbm_gbs"], "dense": {},
+           "grouped": {}, "row_length": {}}
+    for (N, K, kind) in [(6144, 2048, "store"), (2048, 2048, "add"), (11264, 2048, "swiglu"), (2048, 5632, "store"),
+                         (151936, 2048, "store")]:
+        copies = max(2, min(12, int(300e6 // (N * K * 2)) + 1))
+        ws = [torch.randn(N, K, device=dev).to(bf) * 0.05 for _ in range(copies)]
+        a = torch.randn(8, K, device=dev).to(bf)
+        resid = torch.zeros(8, N, device=dev)
+        fn = {"store": lambda c: ops.linear(a, ws[c], None, torch.float32),
+              "add": lambda c: ops.linear_add(a, ws[c], resid),
+              "swiglu": lambda c: ops.linear_swiglu(a, ws[c])}[kind]
+        us = timed(fn, copies)
+        out["dense"][f"{N}x{K}_{kind}"] = {"us": round(us, 2), "tb_s": round(N * K * 2 / us / 1e6, 2)}
+        del ws
+    E, k, H, I = MODEL_A["num_experts"], MODEL_A["num_experts_per_tok"], MODEL_A["hidden_size"], MODEL_A["moe_intermediate_size"]
+    for T in (1, 8, 64):
+        g = torch.Generator().manual_seed(T)
+        ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).cuda()
+        offsets, rows, _ = ops.moe_permute(ids, E)
+        active = int(((offsets[1:] - offsets[:-1]) > 0).sum())
+        wgu = [torch.randn(E, 2 * I, H, device=dev).to(bf) * 0.05 for _ in range(3)]
+        wd = [torch.randn(E, H, I, device=dev).to(bf) * 0.05 for _ in range(3)]
+        h = torch.randn(T, H, device=dev).to(bf)
+        act = ops.grouped_swiglu(h, wgu[0], offsets, rows)
+        u1 = timed(lambda c: ops.grouped_swiglu(h, wgu[c], offsets, rows), 3)
+        u2 = timed(lambda c: ops.grouped_linear(act, wd[c], offsets), 3)
+        out["grouped"][f"tokens{T}"] = {"experts_with_rows": active,
+                                        "gate_up_us": round(u1, 2), "gate_up_tb_s": round(active * 2 * I * H * 2 / u1 / 1e6, 2),
+                                        "down_us": round(u2, 2), "down_tb_s": round(active * I * H * 2 / u2 / 1e6, 2)}
+        del wgu, wd
+    for K in (512, 1024, 1408, 1536, 2048, 2816, 4096):
+        N = (256 * 1024 * 1024 // 2) // K // 16 * 16
+        ws = [torch.randn(N, K, device=dev).to(bf) for _ in range(2)]
+        a = torch.randn(8, K, device=dev).to(bf)
+        us = timed(lambda c: ops.linear(a, ws[c], None, torch.float32), 2)
+        out["row_length"][f"K{K}"] = {"us": round(us, 1), "tb_s": round(N * K * 2 / us / 1e6, 2)}
+        del ws
+    ops.check_errors()
+    return out
+
+
 def layers_that_fit(raw, want, reserve_gb=40.0):
     """As many layers of `raw` (at most `want`) as the free device memory holds beside `reserve_gb` for
     the cache pool, the head, graphs and activations."""
@@ -437,9 +510,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill measurements")
     ap.add_argument("--no-extras", action="store_true", help="skip `sizes_57b` and `serving`")
     ap.add_argument("--only-prefill", action="store_true", help="measure the 2,048-token prefill alone (for profiles)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "sweep", "kernels"],
                     help="serving: the continuous-batching workload on the windowed model, instead of the default line; "
-                         "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own")
+                         "sweep: decode at contexts of 1k to 32k and prefill of longer prompts, a line of its own; "
+                         "kernels: the weight-streaming product alone")
     args = ap.parse_args()
     global FULL_LAYERS, MODEL_NAME
     if args.sizes == "57b":
@@ -463,6 +537,9 @@ def main() -> int:
     pk = peaks()
     if args.workload == "sweep":
         print(json.dumps(run_sweep(args, pk)))
+        return 0
+    if args.workload == "kernels":
+        print(json.dumps(run_kernels(pk)))
         return 0
     max_batch = 64 if not args.no_points else args.batch
     m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk)
