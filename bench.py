@@ -241,13 +241,13 @@ class Measurement:
         # the routing of every captured step: the permutation's offsets stay in the graph's memory
         self.offsets = []
         ops = self.eng.rt.ops
-        permute = ops.moe_permute
+        route = ops.route
 
-        def recording_permute(ids, E):
-            out = permute(ids, E)
-            self.offsets.append(out[0])
+        def recording_route(*a, **kw):
+            out = route(*a, **kw)
+            self.offsets.append(out[3])          # (ids, wts, gate, offsets, rows, dest)
             return out
-        ops.moe_permute = recording_permute
+        ops.route = recording_route
 
     def close(self):
         import gc

@@ -1,11 +1,16 @@
 """Plain, slow Qwen2-MoE: whole sequences, no cache, one function per part.
 
-This file is the oracle of the test-suite.  It rests on the reference's
+This file is the oracle of the test-suite.  It is written from the reference's
 formulas (every function cites the file and lines of vedantnimbarte/dlm it
-restates); the reference itself is Rust and cannot be compiled or imported
-where these tests run, so no output of its code stands behind these numbers.
-It shares no code with ``dlm_b200``: it reads ``config.json`` with ``json`` and
-``model.safetensors`` with the ``safetensors`` package.
+restates).  The reference's Rust cannot be compiled or imported where these
+tests run, but its CUDA model code (src/gpu/kernels.cu) can: outputs of those
+kernels on the tiny configurations, made once on a B200 by
+``tests/golden/make_golden.py``, are committed under ``tests/golden/`` and
+``tests/test_golden.py`` holds this file to them (windows switched off, which
+the reference does not have; the window, the tied head and the tie-break rest
+on the formulas).  It shares no code with ``dlm_b200``: it reads
+``config.json`` with ``json`` and ``model.safetensors`` with the
+``safetensors`` package.
 
 Options the reference lacks (a per-layer sliding window, ``decoder_sparse_step``
 and ``mlp_only_layers``, ``tie_word_embeddings``) follow the rules stated in
