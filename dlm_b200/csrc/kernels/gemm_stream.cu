@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                     if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
                     const unsigned char* st = smem + s * stage_bytes + (size_t)(kw + 8 * t) * 2;
                     // the weights of GB blocks of K are read before their MMAs are issued
-                    constexpr int GB = NT >= 4 ? 2 : 4;
+                    constexpr int GB = 4;
 #pragma unroll
                     for (int b0 = 0; b0 < 8; b0 += GB) {
                         if (b0 < nb) {
@@ -381,9 +381,11 @@ void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, i
     p.expert_offsets = expert_offsets; p.num_experts = num_experts; p.bias = bias; p.out = out; p.ldo = ldo;
     p.M = M; p.N = N; p.K = K;
     p.tiles = (N + RT - 1) / RT;
-    const int nt = rows_per_pass <= 8 ? 1 : (rows_per_pass <= 16 ? 2 : 4);
-    // three stages and the partial sums share 227 KB: the widest pass takes shorter chunks
-    const int kc_max = nt == 4 ? KC_MAX - 256 : KC_MAX;
+    // 8 or 16 rows of A a pass.  (32 rows a pass hold 128 registers of A alone; with 288 threads a block the
+    // register file allows 168 a thread, the compiler spilled, and that variant ran at 40 % of this one's speed:
+    // more rows take more passes instead.)
+    const int nt = rows_per_pass <= 8 ? 1 : 2;
+    const int kc_max = KC_MAX;
     p.n_chunks = (K + kc_max - 1) / kc_max;
     p.kc = ((K + p.n_chunks - 1) / p.n_chunks + 31) / 32 * 32;
     if (p.kc > K) p.kc = K;
@@ -400,8 +402,7 @@ void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, i
     const long long items = (long long)p.tiles * groups;
     const int grid = (int)(items < sm_count() ? items : sm_count());
     if (nt == 1) launch_nt<1>(p, grid, out_dtype, epilogue, stream);
-    else if (nt == 2) launch_nt<2>(p, grid, out_dtype, epilogue, stream);
-    else launch_nt<4>(p, grid, out_dtype, epilogue, stream);
+    else launch_nt<2>(p, grid, out_dtype, epilogue, stream);
     check_launch("gemm_stream");
 }
 
