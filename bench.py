@@ -323,6 +323,30 @@ class Measurement:
                     step_bytes=step_bytes, achieved=achieved, frac=achieved / self.pk["hbm_gbs"],
                     h2d=int(eng.cache.last_h2d_bytes))
 
+    def decode_sampled(self, batch, steps, temperature=0.8):
+        """Tokens a second end to end through run_step with seeded temperature sampling (the sampling kernel
+        and its host side on top of the replayed step)."""
+        from dlm_b200.sampling import SamplingParams
+        torch, eng = self.torch, self.eng
+        ids = [eng.submit(p, SamplingParams(temperature=temperature, seed=i), max_new_tokens=10 ** 6)
+               for i, p in enumerate(self.prompts(batch, self.prompt_len))]
+        started = set()
+        while len(started) < batch:
+            started.update(rid for rid, _ in eng.run_step())
+        for _ in range(3):
+            eng.run_step()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        produced = 0
+        for _ in range(steps):
+            produced += len(eng.run_step())
+        torch.cuda.synchronize()
+        w1 = time.perf_counter()
+        for i in ids:
+            eng.abort(i)
+        eng.scheduler.drain_finished()
+        return produced / (w1 - w0)
+
     def prefill(self, T=2048, repeats=4):
         torch, eng = self.torch, self.eng
         times = []
@@ -581,6 +605,8 @@ def main() -> int:
             fracs[f"decode_b{b}"] = round(r["frac"], 4)
         out["points"] = pts
         out["points_frac"] = fracs          # of the HBM peak, bytes from the experts each step really used
+        out["e2e_sampled"] = {"value": round(m.decode_sampled(args.batch, args.steps), 2), "unit": "tokens/s",
+                              "temperature": 0.8, "batch": args.batch}
         out["prefill"] = m.prefill(2048, repeats=4)
         out["prefill"].pop("all_ms")
     m.eng.rt.ops.check_errors()

@@ -6,7 +6,10 @@
 // index), and "the first place where the running count / mass reaches x" is found by a
 // radix descent over that key, eight bits a pass.  Masses are 40-bit fixed point, so their
 // sums do not depend on the order threads add them in: the same logits and the same uniform
-// number always give the same token.
+// number always give the same token.  A bucket's 64-bit sum is kept as two 32-bit words, added
+// with the hardware's 32-bit shared-memory atomics and an explicit carry (a 64-bit atomic add
+// on shared memory is a compare-and-swap loop, and the first passes put the whole vocabulary
+// into a handful of buckets: that loop was most of the kernel's four milliseconds).
 #include "api.h"
 #include "common.cuh"
 
@@ -119,33 +122,55 @@ struct RowView {
     __device__ unsigned long long mass(float p) const { return (unsigned long long)((double)p * 1099511627776.0); }
 };
 
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned int lo = __shfl_xor_sync(0xffffffffu, (unsigned int)v, o);
+        const unsigned int hi = __shfl_xor_sync(0xffffffffu, (unsigned int)(v >> 32), o);
+        v += ((unsigned long long)hi << 32) | lo;
+    }
+    return v;
+}
+
+// bucket[b] += m, the sum kept as (low word, high word)
+__device__ __forceinline__ void bucket_add(unsigned int* lo, unsigned int* hi, int b, unsigned long long m) {
+    const unsigned int add = (unsigned int)m;
+    const unsigned int old = atomicAdd(&lo[b], add);
+    const unsigned int up = (unsigned int)(m >> 32) + ((old + add < old) ? 1u : 0u);
+    if (up != 0u) atomicAdd(&hi[b], up);
+}
+
 // Sum of masses (or count) of the candidates.
-__device__ unsigned long long block_total(const RowView& rv, bool count, unsigned long long* s_acc) {
-    if (threadIdx.x == 0) *s_acc = 0ull;
-    __syncthreads();
+__device__ unsigned long long block_total(const RowView& rv, bool count, unsigned long long* s_part) {
     unsigned long long local = 0ull;
+#pragma unroll 4
     for (int i = threadIdx.x; i < rv.V; i += blockDim.x) {
         const float v = rv.z[i];
         const float p = rv.prob(v);
         if (rv.ckey(i, v) <= rv.cut && p >= rv.minp_thr) local += count ? 1ull : rv.mass(p);
     }
-    atomicAdd(s_acc, local);
+    local = warp_sum_u64(local);
     __syncthreads();
-    const unsigned long long r = *s_acc;
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = local;
+    __syncthreads();
+    unsigned long long r = 0ull;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) r += s_part[w];
     __syncthreads();
     return r;
 }
 
 // Composite key of the first candidate (in key order) at which the running count / mass reaches `target`.
 __device__ unsigned long long block_select(const RowView& rv, int mode, unsigned long long target,
-                                           unsigned long long* bucket, unsigned long long* s_state) {
+                                           unsigned int* bucket_lo, unsigned int* bucket_hi,
+                                           unsigned long long* s_state) {
     const int total_bits = 32 + rv.idx_bits;
     const int passes = (total_bits + 7) / 8;
     unsigned long long prefix = 0ull, before = 0ull;
     for (int pass = 0; pass < passes; ++pass) {
         const int shift = (passes - 1 - pass) * 8;
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) bucket[b] = 0ull;
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) { bucket_lo[b] = 0u; bucket_hi[b] = 0u; }
         __syncthreads();
+#pragma unroll 4
         for (int i = threadIdx.x; i < rv.V; i += blockDim.x) {
             const float v = rv.z[i];
             const unsigned long long ck = rv.ckey(i, v);
@@ -153,23 +178,26 @@ __device__ unsigned long long block_select(const RowView& rv, int mode, unsigned
             if (pass > 0 && (ck >> (shift + 8)) != (prefix >> (shift + 8))) continue;
             const float p = rv.prob(v);
             if (p < rv.minp_thr) continue;
-            atomicAdd(&bucket[(ck >> shift) & 255ull], mode == COUNT ? 1ull : rv.mass(p));
+            bucket_add(bucket_lo, bucket_hi, (int)((ck >> shift) & 255ull), mode == COUNT ? 1ull : rv.mass(p));
         }
         __syncthreads();
         if (threadIdx.x == 0) {
             unsigned long long run = before;
             int pick = -1, last = -1;
+            unsigned long long last_sum = 0ull;
             for (int b = 0; b < 256; ++b) {
-                if (bucket[b] == 0ull) continue;
+                const unsigned long long sum = ((unsigned long long)bucket_hi[b] << 32) | bucket_lo[b];
+                if (sum == 0ull) continue;
                 last = b;
-                const unsigned long long nxt = run + bucket[b];
+                last_sum = sum;
+                const unsigned long long nxt = run + sum;
                 const bool hit = mode == MASS_GT ? (nxt > target) : (nxt >= target);
                 if (hit) { pick = b; break; }
                 run = nxt;
             }
             if (pick < 0) {            // rounding left the target just beyond the total: the last candidate
                 pick = last < 0 ? 0 : last;
-                run -= (last >= 0 ? bucket[last] : 0ull);
+                run -= (last >= 0 ? last_sum : 0ull);
             }
             s_state[0] = prefix | ((unsigned long long)pick << shift);
             s_state[1] = run;
@@ -188,25 +216,28 @@ sample_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
               const int32_t* __restrict__ seen_tokens, float* __restrict__ scratch) {
     __shared__ float sv[32];
     __shared__ int si[32];
-    __shared__ unsigned long long bucket[256];
+    __shared__ unsigned int bucket_lo[256], bucket_hi[256];
     __shared__ unsigned long long s_state[2];
-    __shared__ unsigned long long s_acc;
+    __shared__ unsigned long long s_part[32];
     const int row = blockIdx.x;
     const float temperature = params[row * 4 + 0], top_p = params[row * 4 + 1], min_p = params[row * 4 + 2],
                 penalty = params[row * 4 + 3];
     const float* lg = logits + (long long)row * V;
-    float* z = scratch + (long long)row * V;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) z[i] = lg[i];
-    __syncthreads();
+    // the penalised logits: a copy in the scratch when there is a penalty, else the logits themselves
+    const float* z = lg;
     if (penalty != 1.0f && seen_offsets != nullptr) {
+        float* zc = scratch + (long long)row * V;
+        for (int i = threadIdx.x; i < V; i += blockDim.x) zc[i] = lg[i];
+        __syncthreads();
         for (int s = seen_offsets[row] + threadIdx.x; s < seen_offsets[row + 1]; s += blockDim.x) {
             const int t = seen_tokens[s];
             if (t >= 0 && t < V) {
-                const float v = z[t];
-                z[t] = v > 0.f ? v / penalty : v * penalty;
+                const float v = zc[t];
+                zc[t] = v > 0.f ? v / penalty : v * penalty;
             }
         }
         __syncthreads();
+        z = zc;
     }
     // the maximum and its first index (the greedy answer)
     float bv = -INFINITY;
@@ -233,17 +264,17 @@ sample_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
     rv.minp_thr = 0.f;
     rv.cut = ~0ull;
     const int k = top_k[row];
-    if (k > 0 && k < V) rv.cut = block_select(rv, COUNT, (unsigned long long)k, bucket, s_state);
+    if (k > 0 && k < V) rv.cut = block_select(rv, COUNT, (unsigned long long)k, bucket_lo, bucket_hi, s_state);
     if (top_p > 0.f && top_p < 1.f) {
-        const unsigned long long Z = block_total(rv, false, &s_acc);
+        const unsigned long long Z = block_total(rv, false, s_part);
         unsigned long long target = (unsigned long long)((double)top_p * (double)Z);
         if (target < 1ull) target = 1ull;
-        rv.cut = block_select(rv, MASS_GE, target, bucket, s_state);
+        rv.cut = block_select(rv, MASS_GE, target, bucket_lo, bucket_hi, s_state);
     }
     if (min_p > 0.f) rv.minp_thr = fminf(min_p, 1.0f);   // the top candidate (probability 1 before scaling) stays
-    const unsigned long long Z = block_total(rv, false, &s_acc);
+    const unsigned long long Z = block_total(rv, false, s_part);
     const unsigned long long target = (unsigned long long)((double)u[row] * (double)Z);
-    const unsigned long long pick = block_select(rv, MASS_GT, target, bucket, s_state);
+    const unsigned long long pick = block_select(rv, MASS_GT, target, bucket_lo, bucket_hi, s_state);
     if (threadIdx.x == 0) {
         int tok = (int)(pick & ((1ull << rv.idx_bits) - 1ull));
         if (tok >= V) tok = mi;

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 _MASK = (1 << 64) - 1
@@ -53,16 +54,33 @@ class SamplingParams:
 
 
 class RequestSampler:
-    """Per-request sampling state: the generator and the set of tokens seen so far."""
+    """Per-request sampling state: the generator and the distinct tokens seen so far (kept as a growing
+    array, so that a step's list of all requests' seen tokens is a concatenation, not a Python loop)."""
 
     def __init__(self, params: SamplingParams, prompt):
         self.params = params
         self.rng = SplitMix64(params.seed)
-        self.seen: dict[int, None] = dict.fromkeys(int(t) for t in prompt) if params.repetition_penalty != 1.0 else {}
+        self._set: set[int] = set()
+        self._arr = np.empty(0, dtype=np.int32)
+        self._n = 0
+        if params.repetition_penalty != 1.0:
+            first = list(dict.fromkeys(int(t) for t in prompt))
+            self._set = set(first)
+            self._arr = np.empty(max(64, 2 * len(first)), dtype=np.int32)
+            self._arr[:len(first)] = first
+            self._n = len(first)
+
+    @property
+    def seen(self) -> np.ndarray:
+        return self._arr[:self._n]
 
     def note(self, token: int) -> None:
-        if self.params.repetition_penalty != 1.0:
-            self.seen[int(token)] = None
+        if self.params.repetition_penalty != 1.0 and int(token) not in self._set:
+            self._set.add(int(token))
+            if self._n == len(self._arr):
+                self._arr = np.concatenate([self._arr, np.empty(len(self._arr), dtype=np.int32)])
+            self._arr[self._n] = int(token)
+            self._n += 1
 
 
 def sample_rows(ops, logits: torch.Tensor, samplers: list[RequestSampler]) -> list[int]:
@@ -74,15 +92,26 @@ def sample_rows(ops, logits: torch.Tensor, samplers: list[RequestSampler]) -> li
     if all(s.params.plain_greedy for s in samplers):
         return ops.argmax(logits).tolist()
     dev = logits.device
-    params = torch.tensor([[s.params.temperature, s.params.top_p, s.params.min_p, s.params.repetition_penalty]
-                           for s in samplers], dtype=torch.float32)
-    top_k = torch.tensor([s.params.top_k for s in samplers], dtype=torch.int32)
-    u = torch.tensor([0.0 if s.params.greedy else s.rng.next_f32() for s in samplers], dtype=torch.float32)
-    offsets, seen = [0], []
+    # one host buffer of 32-bit words for everything the kernel reads besides the logits, one copy:
+    # [N x 4 params | N uniforms | N top_k | N + 1 offsets | seen tokens]
+    offsets = [0]
     for s in samplers:
-        seen.extend(s.seen.keys())
-        offsets.append(len(seen))
-    seen_offsets = torch.tensor(offsets, dtype=torch.int32)
-    seen_tokens = torch.tensor(seen if seen else [0], dtype=torch.int32)
-    out = ops.sample(logits, params.to(dev), top_k.to(dev), u.to(dev), seen_offsets.to(dev), seen_tokens.to(dev))
+        offsets.append(offsets[-1] + len(s.seen))
+    seen = np.concatenate([s.seen for s in samplers]) if offsets[-1] else np.zeros(1, dtype=np.int32)
+    floats = []
+    for s in samplers:
+        floats += [s.params.temperature, s.params.top_p, s.params.min_p, s.params.repetition_penalty]
+    floats += [0.0 if s.params.greedy else s.rng.next_f32() for s in samplers]
+    ints = np.concatenate([np.asarray([s.params.top_k for s in samplers] + offsets, dtype=np.int32), seen])
+    host = torch.empty(len(floats) + len(ints), dtype=torch.int32, pin_memory=(dev.type == "cuda"))
+    host[:len(floats)].view(torch.float32).copy_(torch.tensor(floats, dtype=torch.float32))
+    host[len(floats):].copy_(torch.from_numpy(ints))
+    buf = host.to(dev, non_blocking=True)
+    f = buf[:len(floats)].view(torch.float32)
+    i0 = len(floats)
+    params, u = f[:4 * n].view(n, 4), f[4 * n:5 * n]
+    top_k = buf[i0:i0 + n]
+    seen_offsets = buf[i0 + n:i0 + 2 * n + 1]
+    seen_tokens = buf[i0 + 2 * n + 1:]
+    out = ops.sample(logits, params, top_k, u, seen_offsets, seen_tokens)
     return out.tolist()
