@@ -164,7 +164,8 @@ def run_serving(args) -> dict:
     sampler.start()
     t0 = time.time()
     submitted, produced, steps = 0, 0, 0
-    # per step: device time between two events around it, wall time, and whether it carried prompt tokens
+    # per step: time between two events around it, wall time, and whether it carried prompt tokens (the events
+    # enclose the host's work inside the step too; what the host costs is in the scheduler's counters below)
     records, prompt_seen = [], eng.scheduler.stats().prompt_tokens
     while submitted < n_req or eng.scheduler.has_work():
         if submitted < n_req and steps % 2 == 0:
@@ -190,7 +191,6 @@ def run_serving(args) -> dict:
         kinds[kind].append((e0.elapsed_time(e1), 1e3 * wall))
     step_kinds = {k: {"steps": len(v), "device_ms_mean": round(sum(a for a, _ in v) / len(v), 3),
                       "wall_ms_mean": round(sum(b for _, b in v) / len(v), 3)} for k, v in kinds.items() if v}
-    device_s = sum(e0.elapsed_time(e1) for e0, e1, *_ in records) / 1e3
     time.sleep(0.2)
     sampler.stop()
     clocks = sampler.summary(t0, t1)
@@ -206,10 +206,15 @@ def run_serving(args) -> dict:
         "config": {"model": "Qwen1.5-MoE-A2.7B sizes, window", "requests": n_req, "layers": args.layers,
                    "layers_full": MODEL_A["num_hidden_layers"], "pool_tokens": pool_tokens, "portion": 2048, "page_size": 64,
                    "arrivals": "one request every second step"},
-        "scheduler": {k: st[k] for k in ("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished")},
+        "scheduler": {k: st[k] for k in ("steps", "prompt_tokens", "decode_tokens", "preemptions", "finished",
+                                         "graphs_recorded", "graph_record_seconds", "eager_steps",
+                                         "eager_launch_seconds")},
         "pages": st["pages"], "clocks": clocks,
-        # how much of the wall time the device was at work (events around every step), and the steps by kind
-        "device_busy_frac": round(device_s / (t1 - t0), 4), "step_kinds": step_kinds,
+        # the steps by kind; the host's share: seconds spent recording decode graphs (the device idles) and
+        # launching the steps that are not replayed (the device works meanwhile)
+        "step_kinds": step_kinds,
+        "host": {"graphs_recorded": st["graphs_recorded"], "graph_record_s": st["graph_record_seconds"],
+                 "eager_steps": st["eager_steps"], "eager_launch_s": st["eager_launch_seconds"]},
     }
     del eng
     return line
@@ -621,7 +626,7 @@ def main() -> int:
                           "preemptions": sv["scheduler"]["preemptions"],
                           "high_water_pages": [p["high_water"] for p in sv["pages"]],
                           "pool_pages": [p["total"] for p in sv["pages"]], "complete": sv["complete"],
-                          "device_busy_frac": sv["device_busy_frac"], "step_kinds": sv["step_kinds"],
+                          "host": sv["host"], "step_kinds": sv["step_kinds"],
                           "clocks": sv["clocks"]}
         import gc
 

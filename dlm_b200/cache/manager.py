@@ -61,7 +61,8 @@ class ModelCache:
                     t.name: torch.zeros((self.group_pages[g] + 1, t.heads, ps, t.width), dtype=rt.dtype, device=rt.device)
                     for t in need.tensors}
             if st is not None:
-                self.state[ci] = torch.zeros((self.num_slots, *st.shape), dtype=st.dtype, device=rt.device)
+                # one slot more than requests can hold: the sink that padded rows of a step use
+                self.state[ci] = torch.zeros((self.num_slots + 1, *st.shape), dtype=st.dtype, device=rt.device)
         for ci, (need, st, owner) in enumerate(needs):
             if need is not None and owner != ci:
                 self.call_group[ci] = self.call_group[owner]
@@ -158,8 +159,9 @@ class ModelCache:
 
     def fill_metadata(self, sitems, lay, dev: torch.Tensor) -> None:
         """Packs a step's metadata with a layout fixed earlier and copies it into ``dev`` (a device
-        buffer that a captured graph reads).  The items must give the same layout sizes."""
-        now = self.manager.plan_layout(sitems, lay.table_width[0] if lay.table_width else 0)
+        buffer that a captured graph reads).  The items must give the same layout sizes; fewer
+        requests than the layout has rows are padded with rows that belong to nobody."""
+        now = self.manager.plan_layout(sitems, lay.table_width[0] if lay.table_width else 0, lay.num_requests)
         if (now.total, now.num_tokens, now.num_requests, now.num_wanted) != \
                 (lay.total, lay.num_tokens, lay.num_requests, lay.num_wanted):
             raise ValueError("the step does not fit the fixed metadata layout")

@@ -72,7 +72,8 @@ PYBIND11_MODULE(_dlm_host, m) {
         .def("table", &CacheManager::table)
         .def("stats", &CacheManager::stats)
         .def("free_pages", &CacheManager::free_pages)
-        .def("plan_layout", &CacheManager::plan_layout, py::arg("items"), py::arg("min_table_width") = 0)
+        .def("plan_layout", &CacheManager::plan_layout, py::arg("items"), py::arg("min_table_width") = 0,
+             py::arg("pad_requests") = 0)
         .def("pack",
              [](const CacheManager& c, const std::vector<StepItem>& items, const StepLayout& lay, uintptr_t out,
                 size_t capacity) {

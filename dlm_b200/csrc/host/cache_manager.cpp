@@ -174,10 +174,19 @@ GroupStats CacheManager::stats(int g) const {
     return st;
 }
 
-StepLayout CacheManager::plan_layout(const std::vector<StepItem>& items, int min_table_width) const {
+StepLayout CacheManager::plan_layout(const std::vector<StepItem>& items, int min_table_width, int pad_requests) const {
     StepLayout lay;
     lay.num_groups = (int)groups_.size();
     lay.num_requests = (int)items.size();
+    const int padded = std::max(0, pad_requests - (int)items.size());
+    lay.num_requests += padded;
+    lay.num_tokens += padded;
+    lay.num_single += padded;
+    lay.num_wanted += padded;
+    if (padded > 0) {
+        lay.max_q_len = std::max(lay.max_q_len, 1);
+        lay.max_kv_len = std::max(lay.max_kv_len, 1);
+    }
     lay.table_width.assign(groups_.size(), 1);
     for (auto& it : items) {
         if (!is_open(it.slot)) throw std::invalid_argument("step item names a slot that is not open");
@@ -252,7 +261,25 @@ void CacheManager::pack(const std::vector<StepItem>& items, const StepLayout& la
         }
         t += q;
     }
-    out[lay.off_cu_q + (int)items.size()] = t;
+    // rows that belong to nobody (see plan_layout)
+    for (int r = (int)items.size(); r < lay.num_requests; ++r) {
+        out[lay.off_cu_q + r] = t;
+        out[lay.off_kv_len + r] = 1;
+        out[lay.off_state_slot + r] = (int)slots_.size();
+        out[lay.off_logit_rows + w++] = t;
+        for (size_t g = 0; g < groups_.size(); ++g) {
+            const int width = lay.table_width[g];
+            int32_t* row = out + lay.off_table[g] + r * width;
+            for (int i = 0; i < width; ++i) row[i] = -1;
+            row[0] = groups_[g].num_pages;
+            out[lay.off_slots[g] + t] = groups_[g].num_pages * groups_[g].page_size;
+        }
+        out[lay.off_tokens + t] = 0;
+        out[lay.off_positions + t] = 0;
+        out[lay.off_token_req + t] = r;
+        ++t;
+    }
+    out[lay.off_cu_q + lay.num_requests] = t;
 }
 
 std::string CacheManager::check() const {

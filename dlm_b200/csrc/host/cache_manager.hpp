@@ -96,10 +96,14 @@ public:
     GroupStats stats(int g) const;
     int free_pages(int g) const { return (int)free_[g].size(); }
 
-    // Step metadata.  `plan_layout` sizes the buffer; `pack` fills it.  The
+    // Step metadata.  `plan_layout` sizes the buffer; `pack` fills it.  `pad_requests` > items.size() adds
+    // rows that belong to nobody, so that steps of different numbers of requests share one layout (one
+    // recorded graph): such a row brings one token (id 0, position 0), holds one key, writes it to the sink
+    // page (the page after the pool's last, which the tensors have and the pool never hands out), uses the
+    // sink state slot (index num_slots), and wants its logits like any row; the caller ignores them.  The
     // lengths of the requests must already include this step's tokens (append
     // first).  `min_table_width` > 0 forces a fixed width (for replayed graphs).
-    StepLayout plan_layout(const std::vector<StepItem>& items, int min_table_width = 0) const;
+    StepLayout plan_layout(const std::vector<StepItem>& items, int min_table_width = 0, int pad_requests = 0) const;
     void pack(const std::vector<StepItem>& items, const StepLayout& lay, int32_t* out) const;
 
     // Consistency check used by tests: every page is either free or held by

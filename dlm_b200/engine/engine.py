@@ -10,6 +10,7 @@ budget and decoded tokens of other requests share the step.
 """
 from __future__ import annotations
 
+import time
 from collections import OrderedDict
 from typing import Iterable, Sequence
 
@@ -42,6 +43,17 @@ def make_runtime(dtype="bfloat16", device="cuda:0", ops=None) -> Runtime:
     return Runtime(device, dt, ops)
 
 
+def _row_bucket(rows: int, cap: int) -> int:
+    """The smallest of 1, 2, 3, 4, 6, 8, 12, 16, 24, 32, ... (powers of two and their one-and-a-half) that is
+    at least ``rows``, but no more than ``cap`` (and never less than ``rows``)."""
+    p = 1
+    while True:
+        for b in (p, p + p // 2):
+            if b >= rows:
+                return max(rows, min(b, cap))
+        p *= 2
+
+
 class Engine:
     def __init__(self, config, model, *, page_size: int = 64, num_pages: int | None = None,
                  max_tokens: int | None = None, max_requests: int = 64, max_step_tokens: int = 2048,
@@ -65,6 +77,10 @@ class Engine:
                            and all(part.graph_safe for part in self._all_parts()))
         self.max_graphs = 32
         self._graphs: "OrderedDict[tuple[int, int], dict]" = OrderedDict()
+        self.graphs_recorded = 0          # how many decode graphs were recorded so far
+        self.graph_record_seconds = 0.0   # host time spent recording them
+        self.eager_steps = 0              # steps launched kernel by kernel (not replayed)
+        self.eager_launch_seconds = 0.0   # host time spent launching them (the device works meanwhile)
         self._graph_pool = None
         self._samplers: dict[int, RequestSampler] = {}
         self._results: dict[int, list[int]] = {}
@@ -114,8 +130,12 @@ class Engine:
         return self._run(items)
 
     def _run(self, items) -> torch.Tensor:
+        t0 = time.perf_counter()
         batch = self.cache.make_batch(items)
-        return self.model.step(batch, self.cache)
+        out = self.model.step(batch, self.cache)
+        self.eager_steps += 1
+        self.eager_launch_seconds += time.perf_counter() - t0
+        return out
 
     # ------------------------------------------------- replayed decode steps
     def _run_decode(self, items):
@@ -133,7 +153,11 @@ class Engine:
         while bucket < longest:
             bucket *= 2
         bucket = min(bucket, max(self.max_context, longest))
-        key = (len(items), bucket)
+        # rows are padded up to the next of 1, 2, 3, 4, 6, 8, 12, 16, 24, ... (at most half more), so that a batch
+        # that shrinks request by request does not ask for a new graph at every size
+        rows = len(items)
+        padded = _row_bucket(rows, self.cache.num_slots)
+        key = (padded, bucket)
         sitems = [cache.host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
         ent = self._graphs.get(key)
         if ent is not None:
@@ -141,9 +165,9 @@ class Engine:
             cache.fill_metadata(sitems, ent["layout"], ent["meta"])
             ent["graph"].replay()
             ops.launches += ent["launches"]
-            return ent["logits"], ent["tokens"]
+            return ent["logits"][:rows], ent["tokens"][:rows]
         width = -(-self.max_context // min(cache.group_page_size))
-        lay = cache.manager.plan_layout(sitems, width)
+        lay = cache.manager.plan_layout(sitems, width, padded)
         meta = torch.zeros(lay.total, dtype=torch.int32, device=self.rt.device)
         batch = cache.batch_from_layout(lay, meta)
         batch.max_kv_len = bucket
@@ -151,6 +175,7 @@ class Engine:
         logits = self.model.step(batch, cache)
         tokens = ops.argmax(logits)
         torch.cuda.synchronize()
+        t_rec = time.perf_counter()
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
@@ -158,11 +183,13 @@ class Engine:
         with torch.cuda.graph(graph, pool=self._graph_pool):
             g_logits = self.model.step(batch, cache)
             g_tokens = ops.argmax(g_logits)
+        self.graphs_recorded += 1
+        self.graph_record_seconds += time.perf_counter() - t_rec
         while len(self._graphs) >= self.max_graphs:
             self._graphs.popitem(last=False)
         self._graphs[key] = dict(graph=graph, layout=lay, meta=meta, logits=g_logits, tokens=g_tokens,
                                  launches=ops.launches - before, width=width)
-        return logits, tokens
+        return logits[:rows], tokens[:rows]
 
     # ------------------------------------------------------------- generation
     def submit(self, prompt: Iterable[int], params: SamplingParams | None = None, max_new_tokens: int = 16,
@@ -248,6 +275,8 @@ class Engine:
         pools = self.cache.stats()
         return {"steps": st.steps, "prompt_tokens": st.prompt_tokens, "decode_tokens": st.decode_tokens,
                 "preemptions": st.preemptions, "finished": st.finished,
+                "graphs_recorded": self.graphs_recorded, "graph_record_seconds": round(self.graph_record_seconds, 3),
+                "eager_steps": self.eager_steps, "eager_launch_seconds": round(self.eager_launch_seconds, 3),
                 "pages": [{"total": p.total_pages, "used": p.used_pages, "high_water": p.high_water} for p in pools]}
 
 

@@ -158,3 +158,47 @@ def test_random_orders_lose_no_page(host, seed, window):
     for s in list(live):
         m.close(s)
     assert m.check() == "" and all(m.stats(g).used_pages == 0 for g in range(m.num_groups))
+
+
+def test_padded_rows_belong_to_nobody():
+    """A layout with more rows than requests: the extra rows bring one token each, hold one key on the sink
+    page (the page after the pool's last), use the sink state slot and want their logits; the real rows
+    are packed as without padding."""
+    import numpy as np
+    host = load_host()
+    m = host.CacheManager([host.GroupSpec(16, 0, 10), host.GroupSpec(16, 24, 6)], 4)
+    a, b = m.open(), m.open()
+    m.append([(a, 40), (b, 3)])
+    m.append([(a, 1), (b, 1)])
+    items = [host.StepItem(a, [7], [0]), host.StepItem(b, [9], [0])]
+    plain = m.plan_layout(items, 8)
+    lay = m.plan_layout(items, 8, 4)
+    assert (lay.num_requests, lay.num_tokens, lay.num_wanted, lay.num_single) == (4, 4, 4, 4)
+    buf = np.zeros(lay.total, dtype=np.int32)
+    m.pack(items, lay, buf.ctypes.data, buf.size)
+    ref = np.zeros(plain.total, dtype=np.int32)
+    m.pack(items, plain, ref.ctypes.data, ref.size)
+
+    def part(l, arr, off, n):
+        return arr[off:off + n].tolist()
+    assert part(lay, buf, lay.off_tokens, 4) == [7, 9, 0, 0]
+    assert part(lay, buf, lay.off_positions, 4) == [40, 3, 0, 0]
+    assert part(lay, buf, lay.off_cu_q, 5) == [0, 1, 2, 3, 4]
+    assert part(lay, buf, lay.off_kv_len, 4) == [41, 4, 1, 1]
+    assert part(lay, buf, lay.off_state_slot, 4) == [a, b, 4, 4]
+    assert part(lay, buf, lay.off_logit_rows, 4) == [0, 1, 2, 3]
+    for g, (pages, ps) in enumerate([(10, 16), (6, 16)]):
+        assert part(lay, buf, lay.off_slots[g], 2) == part(plain, ref, plain.off_slots[g], 2)
+        assert part(lay, buf, lay.off_slots[g] + 2, 2) == [pages * ps, pages * ps]
+        w = lay.table_width[g]
+        rows = buf[lay.off_table[g]:lay.off_table[g] + 4 * w].reshape(4, w)
+        assert rows[:2].tolist() == ref[plain.off_table[g]:plain.off_table[g] + 2 * w].reshape(2, w).tolist()
+        assert rows[2].tolist() == [pages] + [-1] * (w - 1) and rows[3].tolist() == rows[2].tolist()
+    assert m.check() == ""
+
+
+def test_row_buckets():
+    from dlm_b200.engine.engine import _row_bucket
+    assert sorted({_row_bucket(r, 64) for r in range(1, 65)}) == [1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64]
+    assert [_row_bucket(r, 64) for r in (1, 5, 7, 9, 33, 49, 64)] == [1, 6, 8, 12, 48, 64, 64]
+    assert _row_bucket(5, 5) == 5 and _row_bucket(40, 40) == 40
