@@ -603,13 +603,15 @@ def main() -> int:
         "load_s": round(m.load_s, 1),
     }
     if not args.no_points:
-        pts, fracs = {}, {f"decode_b{args.batch}": round(main_run["frac"], 4)}
+        pts, fracs, e2e = {}, {f"decode_b{args.batch}": round(main_run["frac"], 4)}, {}
         for b in (1, 64):
             r = m.decode(b, max(8, args.steps // 2), 3)
             pts[f"decode_b{b}"] = round(r["tok_s"], 2)
             fracs[f"decode_b{b}"] = round(r["frac"], 4)
+            e2e[f"decode_b{b}"] = round(r["e2e_tok_s"], 2)
         out["points"] = pts
         out["points_frac"] = fracs          # of the HBM peak, bytes from the experts each step really used
+        out["points_e2e"] = e2e             # the same points through run_step, host tokens in and out
         out["e2e_sampled"] = {"value": round(m.decode_sampled(args.batch, args.steps), 2), "unit": "tokens/s",
                               "temperature": 0.8, "batch": args.batch}
         out["prefill"] = m.prefill(2048, repeats=4)
