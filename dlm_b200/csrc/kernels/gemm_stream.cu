@@ -9,9 +9,11 @@
 // bulk copy costs about 60 ns whatever its size; with one copy per row a tile could not take less than a
 // microsecond, which held products with rows shorter than 1,500 elements below the memory's bandwidth.)  Eight consumer warps split a chunk along K; each multiplies its slice by the rows of A,
 // which it holds in registers, in tensor-core MMAs with the roles swapped (16 rows of W are the MMA's
-// M, 8 rows of A its N; mma.sync m16n8k16, bfloat16 in, 32-bit accumulation), and the eight partial
-// sums of a tile are added in a fixed order through shared memory, one tile late, so that no warp
-// waits for the slowest.  A result does not depend on what else was in the batch.
+// M, 8 rows of A its N; mma.sync m16n8k16, bfloat16 in, 32-bit accumulation), and leaves its partial
+// sums in shared memory (two buffers, handed over through mbarriers).  A tenth warp adds the eight partial
+// sums of a tile in a fixed order, applies the epilogue and stores, while the consumers are at the next
+// tile: no consumer waits for the slowest one or pays for the sums (when every consumer warp joined in
+// them, that was 430 clocks of a tile's 2,000).  A result does not depend on what else was in the batch.
 //
 // K is walked in blocks of 32.  Lane (g = lane / 4, t = lane % 4) takes the 8 consecutive elements
 // 8t..8t+7 of rows g and g + 8 of the weight tile and of row g of A; the two MMAs of a block take
@@ -44,7 +46,7 @@ namespace {
 using namespace tc5;      // mbarrier helpers with bounded waits
 
 constexpr int CW = 8;                        // consumer warps
-constexpr int THREADS = (CW + 1) * 32;       // + the producer warp
+constexpr int THREADS = (CW + 2) * 32;       // + the producer warp + the warp that finishes tiles
 constexpr int RT = 16;                       // rows of W per tile
 constexpr int STAGES = 3;
 constexpr int KC_MAX = 2048;                 // most elements of a row per stage
@@ -102,6 +104,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
     __shared__ __align__(8) uint64_t full_bar[STAGES];     // a stage has arrived
     __shared__ __align__(8) uint64_t empty_bar[STAGES];    // all consumer warps have read a stage
     __shared__ __align__(8) uint64_t red_full[2];          // partial sums of a tile written by all consumer warps
+    __shared__ __align__(8) uint64_t red_empty[2];         // ... and added up and stored: the buffer is free again
     __shared__ int s_active[MAX_ACTIVE];
     __shared__ int s_n_active, s_abort;
 
@@ -109,6 +112,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
     const size_t stage_bytes = (size_t)RT * p.pitch;
     float* red = reinterpret_cast<float*>(smem + STAGES * stage_bytes);      // [2][CW][16][MP + 1]
     const bool grouped = p.expert_offsets != nullptr;
+    const bool early = !grouped;       // grouped: every thread has waited for the kernel before this one below
     volatile int* abort_flag = &s_abort;
 
     if (tid == 0) {
@@ -117,6 +121,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], CW); }
         mbar_init(&red_full[0], CW);
         mbar_init(&red_full[1], CW);
+        mbar_init(&red_empty[0], 1);
+        mbar_init(&red_empty[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (grouped) {
@@ -183,7 +189,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                     if (mbar_try_wait(&full_bar[j % STAGES], (j / STAGES) & 1)) break;
             }
         }
-    } else {
+    } else if (warp < CW) {
         // ----------------------------------------------------------------- consumers
         if (!grouped) {
             dep_wait();
@@ -196,42 +202,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
         bool ok = true;
         uint4 xb[NT][8];
         long long held = -1;                             // (first row, pass) whose rows of A are in xb (one chunk per tile)
-        struct Done { int out_row0, m_here, n_base; };   // where a finished tile's sums go
-        Done prev{0, 0, 0};
-        // adds the eight partial sums of tile number `e` in a fixed order and stores the results
-        auto finish_tile = [&](uint32_t e, const Done& d) -> bool {
-            if (!mbar_wait(&red_full[e & 1], (e >> 1) & 1, abort_flag)) return false;
-            const float* rb = red + (size_t)(e & 1) * CW * 16 * (MP + 1);
-            if (EPI == EPI_SWIGLU) {
-                // element = (row of A, pair of weight rows)
-                for (int i = tid; i < MP * 8; i += CW * 32) {
-                    const int pr = i & 7, m = i >> 3;
-                    const int n = d.n_base + 2 * pr;
-                    if (m >= d.m_here || n + 1 >= p.N) continue;
-                    float gate = 0.f, up = 0.f;
-#pragma unroll
-                    for (int ww = 0; ww < CW; ++ww) {
-                        gate += rb[((size_t)ww * 16 + 2 * pr) * (MP + 1) + m];
-                        up += rb[((size_t)ww * 16 + 2 * pr + 1) * (MP + 1) + m];
-                    }
-                    static_cast<TOut*>(p.out)[(long long)(d.out_row0 + m) * p.ldo + (n >> 1)] =
-                        from_f32<TOut>(silu_f(gate) * up);
-                }
-            } else {
-                for (int i = tid; i < MP * 16; i += CW * 32) {
-                    const int row = i & 15, m = i >> 4;
-                    const int n = d.n_base + row;
-                    if (m >= d.m_here || n >= p.N) continue;
-                    float v = 0.f;
-#pragma unroll
-                    for (int ww = 0; ww < CW; ++ww) v += rb[((size_t)ww * 16 + row) * (MP + 1) + m];
-                    const long long o = (long long)(d.out_row0 + m) * p.ldo + n;
-                    if (EPI == EPI_ADD) static_cast<float*>(p.out)[o] += v;
-                    else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(v + (p.bias ? p.bias[n] : 0.f));
-                }
-            }
-            return true;
-        };
         for (int item = item_begin; item < item_end && ok; ++item) {
             const Work wk = get_work(p, s_active, item);
             const int passes = (wk.m_count + MP - 1) / MP;
@@ -301,12 +271,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                     if (lane == 0) mbar_arrive(&empty_bar[s]);
                 }
                 if (!ok) break;
-                // The sums of the tile before this one are finished now, one tile late, so that nobody waits
-                // for the slowest warp: its partial sums have long been written.
-                if (ep > 0 && !finish_tile(ep - 1, prev)) { ok = false; break; }
-                // Partial sums to shared memory: red[ep % 2][warp][weight row][row of A].  The buffer's last
-                // readers (tile ep - 2) were done before they wrote the partial sums of tile ep - 1, which
-                // finish_tile has just waited for.
+                // Partial sums to shared memory: red[ep % 2][warp][weight row][row of A], once the finishing warp
+                // has read what tile ep - 2 left there (it has, as a rule, long ago).
+                if (ep >= 2 && !mbar_wait(&red_empty[ep & 1], ((ep >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 float* mine = red + ((size_t)(ep & 1) * CW + warp) * 16 * (MP + 1);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
@@ -317,11 +284,57 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_full[ep & 1]);
-                prev = Done{wk.row0 + m0, min(MP, wk.m_count - m0), wk.tile * RT};
                 ++ep;
             }
         }
-        if (ok && ep > 0) finish_tile(ep - 1, prev);
+    } else {
+        // ------------------------------------------------------- the warp that finishes tiles
+        // It adds the eight partial sums of a tile in a fixed order, applies the epilogue and stores, while the
+        // consumer warps are at the next tile: none of them waits for the slowest one.
+        if (early) dep_wait();
+        uint32_t e = 0;
+        bool ok = true;
+        for (int item = item_begin; item < item_end && ok; ++item) {
+            const Work wk = get_work(p, s_active, item);
+            const int passes = (wk.m_count + MP - 1) / MP;
+            for (int pass = 0; pass < passes; ++pass, ++e) {
+                const int out_row0 = wk.row0 + pass * MP, m_here = min(MP, wk.m_count - pass * MP), n_base = wk.tile * RT;
+                if (!mbar_wait(&red_full[e & 1], (e >> 1) & 1, abort_flag)) { ok = false; break; }
+                const float* rb = red + (size_t)(e & 1) * CW * 16 * (MP + 1);
+                if (EPI == EPI_SWIGLU) {
+                    // element = (row of A, pair of weight rows)
+#pragma unroll
+                    for (int i = lane; i < MP * 8; i += 32) {
+                        const int pr = i & 7, m = i >> 3;
+                        const int n = n_base + 2 * pr;
+                        if (m >= m_here || n + 1 >= p.N) continue;
+                        float gate = 0.f, up = 0.f;
+#pragma unroll
+                        for (int ww = 0; ww < CW; ++ww) {
+                            gate += rb[((size_t)ww * 16 + 2 * pr) * (MP + 1) + m];
+                            up += rb[((size_t)ww * 16 + 2 * pr + 1) * (MP + 1) + m];
+                        }
+                        static_cast<TOut*>(p.out)[(long long)(out_row0 + m) * p.ldo + (n >> 1)] =
+                            from_f32<TOut>(silu_f(gate) * up);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = lane; i < MP * 16; i += 32) {
+                        const int row = i & 15, m = i >> 4;
+                        const int n = n_base + row;
+                        if (m >= m_here || n >= p.N) continue;
+                        float v = 0.f;
+#pragma unroll
+                        for (int ww = 0; ww < CW; ++ww) v += rb[((size_t)ww * 16 + row) * (MP + 1) + m];
+                        const long long o = (long long)(out_row0 + m) * p.ldo + n;
+                        if (EPI == EPI_ADD) static_cast<float*>(p.out)[o] += v;
+                        else static_cast<TOut*>(p.out)[o] = from_f32<TOut>(v + (p.bias ? p.bias[n] : 0.f));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_empty[e & 1]);
+            }
+        }
     }
     __syncthreads();
     if (tid == 0 && s_abort) *p.err = 5;
