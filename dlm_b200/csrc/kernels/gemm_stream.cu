@@ -32,6 +32,7 @@
 // The kernel may start while the kernel before it ends (see dep_wait in common.cuh): the producer of
 // a dense product starts to fetch weights, which no kernel writes, before the activations are there.
 #include <cstdlib>
+#include <type_traits>
 
 #include "api.h"
 #include "common.cuh"
@@ -97,7 +98,7 @@ __device__ __forceinline__ Work get_work(const StreamParams& p, const int* s_act
     return wk;
 }
 
-template <int NT, int EPI, typename TOut>
+template <int NT, int NCH, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p) {
     constexpr int MP = 8 * NT;                       // rows of A per pass
     extern __shared__ __align__(128) unsigned char smem[];
@@ -195,80 +196,106 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
             dep_wait();
             dep_launch_next();
         }
+        // This lane's pieces of the rows of A of the current (expert, pass), for NCH chunks of K.  A tile of one
+        // chunk, or of two with NCH = 2: they stay in registers from tile to tile.  More chunks than NCH: they are
+        // fetched again at every chunk, and those loads queue in L2 behind the weights in flight (rows of 2,560
+        // and 3,584 elements streamed at 2.8 TB/s that way; NCH = 2 with 8 rows a pass is for them).
+        uint4 xb[NT][8 * NCH];
+        const bool held_for_tile = p.n_chunks <= NCH;
+        long long held = -1;                             // (first row, pass) whose rows of A are in xb
         const int g = lane >> 2, t = lane & 3;
         const int kw = warp * p.slice;                   // this warp's first element within a chunk
         const int nb = p.slice >> 5;                     // its blocks of 32 elements
+        // fills xb[.][XO .. XO + 7] with the pieces of chunk c
+        auto load_rows = [&](const Work& wk, int m0, int c, auto xo) {
+            constexpr int XO = decltype(xo)::value;
+            const int k0 = c * p.kc;
+            const int len = min(p.kc, p.K - k0);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int m = m0 + nt * 8 + g;
+                const __nv_bfloat16* arow = nullptr;
+                if (m < wk.m_count) {
+                    const int src = p.a_rows ? p.a_rows[wk.row0 + m] : wk.row0 + m;
+                    arow = p.a + (long long)src * p.lda + k0 + kw + 8 * t;
+                }
+#pragma unroll
+                for (int b = 0; b < 8; ++b) {
+                    xb[nt][XO + b] = make_uint4(0, 0, 0, 0);
+                    if (b < nb && arow != nullptr && kw + 32 * b + 8 * t < len)
+                        xb[nt][XO + b] = __ldg(reinterpret_cast<const uint4*>(arow + 32 * b));
+                }
+            }
+        };
         uint32_t it = 0, ep = 0;
         bool ok = true;
-        uint4 xb[NT][8];
-        long long held = -1;                             // (first row, pass) whose rows of A are in xb (one chunk per tile)
+        float acc[NT][2][4];
+        // one chunk of a tile: waits for its stage, multiplies, gives the stage back
+        auto do_chunk = [&](int c, auto xo) -> bool {
+            constexpr int XO = decltype(xo)::value;
+            const int len = min(p.kc, p.K - c * p.kc);
+            const uint32_t s = it % STAGES;
+            if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) return false;
+            const unsigned char* st = smem + s * stage_bytes + (size_t)(kw + 8 * t) * 2;
+            // the weights of GB blocks of K are read before their MMAs are issued
+            constexpr int GB = 4;
+#pragma unroll
+            for (int b0 = 0; b0 < 8; b0 += GB) {
+                if (b0 < nb) {
+                    uint4 wa[GB], wb[GB];
+#pragma unroll
+                    for (int j = 0; j < GB; ++j) {
+                        const int b = b0 + j;
+                        wa[j] = wb[j] = make_uint4(0, 0, 0, 0);
+                        // K is a multiple of 8: a lane's 8 elements are all in or all out
+                        if (b < nb && kw + 32 * b + 8 * t < len) {
+                            wa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * p.pitch + 64 * b);
+                            wb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * p.pitch + 64 * b);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < GB; ++j) {
+                        const int b = b0 + j;
+                        if (b < nb) {
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                mma_free(acc[nt][0], wa[j].x, wb[j].x, wa[j].y, wb[j].y, xb[nt][XO + b].x, xb[nt][XO + b].y);
+                                mma_free(acc[nt][1], wa[j].z, wb[j].z, wa[j].w, wb[j].w, xb[nt][XO + b].z, xb[nt][XO + b].w);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+            ++it;
+            return true;
+        };
+        using X0 = std::integral_constant<int, 0>;
+        using X1 = std::integral_constant<int, NCH == 2 ? 8 : 0>;
         for (int item = item_begin; item < item_end && ok; ++item) {
             const Work wk = get_work(p, s_active, item);
             const int passes = (wk.m_count + MP - 1) / MP;
             for (int pass = 0; pass < passes && ok; ++pass) {
                 const int m0 = pass * MP;
-                float acc[NT][2][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[nt][0][i] = acc[nt][1][i] = 0.f;
-                for (int c = 0; c < p.n_chunks; ++c, ++it) {
-                    const int k0 = c * p.kc;
-                    const int len = min(p.kc, p.K - k0);
-                    // this lane's pieces of the rows of A
-                    const long long key = ((long long)wk.row0 << 20) | (long long)pass;
-                    if (p.n_chunks > 1 || key != held) {
+                const long long key = ((long long)wk.row0 << 20) | (long long)pass;
+                if (held_for_tile) {
+                    if (key != held) {
                         held = key;
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            const int m = m0 + nt * 8 + g;
-                            const __nv_bfloat16* arow = nullptr;
-                            if (m < wk.m_count) {
-                                const int src = p.a_rows ? p.a_rows[wk.row0 + m] : wk.row0 + m;
-                                arow = p.a + (long long)src * p.lda + k0 + kw + 8 * t;
-                            }
-#pragma unroll
-                            for (int b = 0; b < 8; ++b) {
-                                xb[nt][b] = make_uint4(0, 0, 0, 0);
-                                if (b < nb && arow != nullptr && kw + 32 * b + 8 * t < len)
-                                    xb[nt][b] = __ldg(reinterpret_cast<const uint4*>(arow + 32 * b));
-                            }
-                        }
+                        load_rows(wk, m0, 0, X0{});
+                        if (NCH == 2 && p.n_chunks == 2) load_rows(wk, m0, 1, X1{});
                     }
-                    const uint32_t s = it % STAGES;
-                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
-                    const unsigned char* st = smem + s * stage_bytes + (size_t)(kw + 8 * t) * 2;
-                    // the weights of GB blocks of K are read before their MMAs are issued
-                    constexpr int GB = 4;
-#pragma unroll
-                    for (int b0 = 0; b0 < 8; b0 += GB) {
-                        if (b0 < nb) {
-                            uint4 wa[GB], wb[GB];
-#pragma unroll
-                            for (int j = 0; j < GB; ++j) {
-                                const int b = b0 + j;
-                                wa[j] = wb[j] = make_uint4(0, 0, 0, 0);
-                                // K is a multiple of 8: a lane's 8 elements are all in or all out
-                                if (b < nb && kw + 32 * b + 8 * t < len) {
-                                    wa[j] = *reinterpret_cast<const uint4*>(st + (size_t)g * p.pitch + 64 * b);
-                                    wb[j] = *reinterpret_cast<const uint4*>(st + (size_t)(g + 8) * p.pitch + 64 * b);
-                                }
-                            }
-#pragma unroll
-                            for (int j = 0; j < GB; ++j) {
-                                const int b = b0 + j;
-                                if (b < nb) {
-#pragma unroll
-                                    for (int nt = 0; nt < NT; ++nt) {
-                                        mma_free(acc[nt][0], wa[j].x, wb[j].x, wa[j].y, wb[j].y, xb[nt][b].x, xb[nt][b].y);
-                                        mma_free(acc[nt][1], wa[j].z, wb[j].z, wa[j].w, wb[j].w, xb[nt][b].z, xb[nt][b].w);
-                                    }
-                                }
-                            }
-                        }
+                    ok = do_chunk(0, X0{});
+                    if (NCH == 2 && p.n_chunks == 2 && ok) ok = do_chunk(1, X1{});
+                } else {
+                    for (int c = 0; c < p.n_chunks && ok; ++c) {
+                        load_rows(wk, m0, c, X0{});
+                        ok = do_chunk(c, X0{});
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_bar[s]);
                 }
                 if (!ok) break;
                 // Partial sums to shared memory: red[ep % 2][warp][weight row][row of A], once the finishing warp
@@ -340,23 +367,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
     if (tid == 0 && s_abort) *p.err = 5;
 }
 
-template <int NT, int EPI, typename TOut>
+template <int NT, int NCH, int EPI, typename TOut>
 void launch_one(const StreamParams& p, int grid, cudaStream_t stream) {
     const size_t smem = (size_t)STAGES * RT * p.pitch + 2 * sizeof(float) * CW * 16 * (8 * NT + 1);
-    auto kern = gemm_stream_kernel<NT, EPI, TOut>;
+    auto kern = gemm_stream_kernel<NT, NCH, EPI, TOut>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_dep(kern, grid, THREADS, smem, stream, p);
 }
 
-template <int NT>
+template <int NT, int NCH>
 void launch_nt(const StreamParams& p, int grid, int out_dtype, int epilogue, cudaStream_t stream) {
     const bool f32 = out_dtype == F32;
     switch (epilogue) {
-        case EPI_STORE: if (f32) launch_one<NT, EPI_STORE, float>(p, grid, stream);
-                        else launch_one<NT, EPI_STORE, __nv_bfloat16>(p, grid, stream); break;
-        case EPI_ADD: launch_one<NT, EPI_ADD, float>(p, grid, stream); break;
-        default: if (f32) launch_one<NT, EPI_SWIGLU, float>(p, grid, stream);
-                 else launch_one<NT, EPI_SWIGLU, __nv_bfloat16>(p, grid, stream); break;
+        case EPI_STORE: if (f32) launch_one<NT, NCH, EPI_STORE, float>(p, grid, stream);
+                        else launch_one<NT, NCH, EPI_STORE, __nv_bfloat16>(p, grid, stream); break;
+        case EPI_ADD: launch_one<NT, NCH, EPI_ADD, float>(p, grid, stream); break;
+        default: if (f32) launch_one<NT, NCH, EPI_SWIGLU, float>(p, grid, stream);
+                 else launch_one<NT, NCH, EPI_SWIGLU, __nv_bfloat16>(p, grid, stream); break;
     }
 }
 
@@ -397,9 +424,11 @@ void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, i
     // 8 or 16 rows of A a pass.  (32 rows a pass hold 128 registers of A alone; with 288 threads a block the
     // register file allows 168 a thread, the compiler spilled, and that variant ran at 40 % of this one's speed:
     // more rows take more passes instead.)
-    const int nt = rows_per_pass <= 8 ? 1 : 2;
-    const int kc_max = KC_MAX;
-    p.n_chunks = (K + kc_max - 1) / kc_max;
+    p.n_chunks = (K + KC_MAX - 1) / KC_MAX;
+    // Rows of two chunks: a lane holds its pieces of 8 rows of A for both chunks (as many registers as 16 rows
+    // of one chunk); more rows take more passes, whose weights come from L2.
+    const bool hold2 = p.n_chunks == 2 && rows_per_pass <= 8;
+    const int nt = (rows_per_pass <= 8 || hold2) ? 1 : 2;
     p.kc = ((K + p.n_chunks - 1) / p.n_chunks + 31) / 32 * 32;
     if (p.kc > K) p.kc = K;
     p.slice = ((p.kc + CW - 1) / CW + 31) / 32 * 32;
@@ -414,8 +443,9 @@ void gemm_stream(const void* a, int lda, const int32_t* a_rows, const void* w, i
     const int groups = expert_offsets ? (num_experts < M ? num_experts : M) : 1;
     const long long items = (long long)p.tiles * groups;
     const int grid = (int)(items < sm_count() ? items : sm_count());
-    if (nt == 1) launch_nt<1>(p, grid, out_dtype, epilogue, stream);
-    else launch_nt<2>(p, grid, out_dtype, epilogue, stream);
+    if (hold2) launch_nt<1, 2>(p, grid, out_dtype, epilogue, stream);
+    else if (nt == 1) launch_nt<1, 1>(p, grid, out_dtype, epilogue, stream);
+    else launch_nt<2, 1>(p, grid, out_dtype, epilogue, stream);
     check_launch("gemm_stream");
 }
 
