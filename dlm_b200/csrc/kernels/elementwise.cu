@@ -94,10 +94,10 @@ template <> struct Out4<__nv_bfloat16> {
 
 // The sum of squares of a row has one order, whoever computes it: the row's elements (VEC: its groups of four)
 // are dealt round-robin to 8 x 32 partial sums, partial sum (v, l) takes items 32 v + l, + 256, + 512, ...; each
-// v's 32 partial sums go through a shuffle tree; the eight results are added in order.  WIDE: the eight warps of
-// a block share one row, warp v keeps the partial sums (v, .); else one warp keeps all eight sets for its row and
-// a block holds several rows.  So a row's result does not depend on how many rows the launch has.
-template <typename TOut, bool VEC, bool WIDE>
+// v's 32 partial sums go through a shuffle tree; the eight results are added in order.  The eight warps of a
+// block share one row, warp v keeps the partial sums (v, .).  (A warp per row, eight rows to a block, was
+// measured for launches of 2,048 rows: 2 us slower a launch.)
+template <typename TOut, bool VEC>
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut* out,
                                const int32_t* rows, int n_rows, int H, float eps) {
     __shared__ float s_part[8];
@@ -107,7 +107,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut
     dep_wait();
     dep_launch_next();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r = WIDE ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + warp;
+    const int r = blockIdx.x;
     if (r >= n_rows) return;
     const float* xr = x + (long long)(rows ? rows[r] : r) * H;
     TOut* o = out + (long long)r * H;
@@ -121,31 +121,16 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut
         }
         return acc;
     };
+    float part = 0.f;
+    for (int i = 32 * warp + lane; i < items; i += 256) part = square(i, part);
+    part = warp_sum(part);
+    if (lane == 0) s_part[warp] = part;
+    __syncthreads();
     float ss = 0.f;
-    if (WIDE) {
-        float part = 0.f;
-        for (int i = 32 * warp + lane; i < items; i += 256) part = square(i, part);
-        part = warp_sum(part);
-        if (lane == 0) s_part[warp] = part;
-        __syncthreads();
 #pragma unroll
-        for (int v = 0; v < 8; ++v) ss += s_part[v];
-    } else {
-        float part[8];
-#pragma unroll
-        for (int v = 0; v < 8; ++v) part[v] = 0.f;
-        for (int base = 0; base < items; base += 256) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-                const int i = base + 32 * v + lane;
-                if (i < items) part[v] = square(i, part[v]);
-            }
-        }
-#pragma unroll
-        for (int v = 0; v < 8; ++v) ss += warp_sum(part[v]);
-    }
+    for (int v = 0; v < 8; ++v) ss += s_part[v];
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-    const int first = WIDE ? threadIdx.x : lane, step = WIDE ? 256 : 32;
+    const int first = threadIdx.x, step = 256;
     if (VEC) {
         const float4* x4 = reinterpret_cast<const float4*>(xr);
         const float4* w4 = reinterpret_cast<const float4*>(w);
@@ -379,21 +364,14 @@ void embed(const int32_t* tokens, const void* table, float* out, int T, int H, i
 void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int n_rows, int H, float eps,
              int out_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return;
-    // few rows: the eight warps of a block share a row; many rows: a warp each, eight rows to a block
-    const bool wide = n_rows < 1024;
-    const int grid = wide ? n_rows : (n_rows + 7) / 8, threads = 256;
+    const int grid = n_rows, threads = 256;
     const bool vec = H % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
                                      reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-#define DLM_NORM(TOUT, VEC, WIDE)                                                                              \
-    launch_dep(rmsnorm_kernel<TOUT, VEC, WIDE>, grid, threads, 0, stream, x, w, static_cast<TOUT*>(out), rows, \
+#define DLM_NORM(TOUT, VEC)                                                                              \
+    launch_dep(rmsnorm_kernel<TOUT, VEC>, grid, threads, 0, stream, x, w, static_cast<TOUT*>(out), rows, \
                n_rows, H, eps)
-    if (out_dtype == F32) {
-        if (vec) { if (wide) DLM_NORM(float, true, true); else DLM_NORM(float, true, false); }
-        else { if (wide) DLM_NORM(float, false, true); else DLM_NORM(float, false, false); }
-    } else {
-        if (vec) { if (wide) DLM_NORM(__nv_bfloat16, true, true); else DLM_NORM(__nv_bfloat16, true, false); }
-        else { if (wide) DLM_NORM(__nv_bfloat16, false, true); else DLM_NORM(__nv_bfloat16, false, false); }
-    }
+    if (out_dtype == F32) { if (vec) DLM_NORM(float, true); else DLM_NORM(float, false); }
+    else { if (vec) DLM_NORM(__nv_bfloat16, true); else DLM_NORM(__nv_bfloat16, false); }
 #undef DLM_NORM
     check_launch("rmsnorm");
 }
