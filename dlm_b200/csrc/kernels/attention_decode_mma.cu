@@ -572,8 +572,13 @@ void attention_decode_mma(const void* q, const void* k_cache, const void* v_cach
         DecodeTmaParams p{static_cast<const __nv_bfloat16*>(q), block_table, table_width, cu_q, kv_len, part_o, part_ml, nh,
                           nkv, page_size, shift, total_pages, window, scale * 1.4426950408889634f, splits, head_passes,
                           static_cast<__nv_bfloat16*>(out), fuse_merge, error_flag_ptr()};
-        const bool done = hd == 64 ? launch_tma<64, 3>(tma_grid, stream, k_cache, v_cache, p)
-                                   : launch_tma<128, 3>(tma_grid, stream, k_cache, v_cache, p);
+        // Blocks that have a multiprocessor to themselves keep six tiles in flight instead of three (8 requests
+        // of 8,192 tokens: 4.72 -> 4.57 ms a step; of 1,030: 3.245 -> 3.235).
+        const bool alone = per_split * splits <= n_sm;
+        const bool done = hd == 64 ? (alone ? launch_tma<64, 6>(tma_grid, stream, k_cache, v_cache, p)
+                                            : launch_tma<64, 3>(tma_grid, stream, k_cache, v_cache, p))
+                                   : (alone ? launch_tma<128, 6>(tma_grid, stream, k_cache, v_cache, p)
+                                            : launch_tma<128, 3>(tma_grid, stream, k_cache, v_cache, p));
         if (done) {
             check_launch("attention_decode_tma");
             if (!fuse_merge) attention_decode_merge(part_o, part_ml, cu_q, out, R, nh, hd, splits, BF16, stream);
