@@ -68,9 +68,11 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
                  float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
                  int score_fn, float scale, const float* select_bias, cudaStream_t stream);
 
-// router_topk followed by moe_permute (below), in one launch when the step has few tokens (T <= 16; measured: beyond that
-// the one block that chooses for every token is slower than the separate kernels).
-void router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
+// router_topk followed by moe_permute (below).  One launch up to 16 tokens (blocks of 8 experts per token, the
+// block that finishes last chooses for every token and groups) and from 17 to 48 tokens (a block per token
+// computes all its logits and chooses; the last block groups); three launches from 49 tokens on.  Returns the
+// number of launches.
+int router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
                          float* wts, float* gate, int32_t* offsets, int32_t* rows, int32_t* dest, int T, int H, int E,
                          int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,
                          const float* select_bias, cudaStream_t stream);

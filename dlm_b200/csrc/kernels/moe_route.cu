@@ -266,6 +266,7 @@ router_select_kernel(const float* logits, int32_t* ids, float* wts,
 
 // Groups n (token, choice) pairs by expert with the threads of one block: counts, an exclusive scan, and the
 // rows.  `sm`: 2 * E ints of shared memory.  Every thread of the block calls it.
+template <bool COHERENT = false>
 __device__ __forceinline__ void permute_block(int* sm, const int32_t* ids, int n, int k, int E, int32_t* offsets,
                                               int32_t* rows, int32_t* dest, int* err) {
     int* count = sm;          // [E]
@@ -274,7 +275,7 @@ __device__ __forceinline__ void permute_block(int* sm, const int32_t* ids, int n
     for (int e = tid; e < E; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int i = tid; i < n; i += blockDim.x) {
-        const int e = ids[i];
+        const int e = COHERENT ? __ldcg(ids + i) : ids[i];      // COHERENT: written by other blocks of this launch
         if (e >= 0 && e < E) atomicAdd(&count[e], 1);
         else *err = 4;
     }
@@ -290,7 +291,7 @@ __device__ __forceinline__ void permute_block(int* sm, const int32_t* ids, int n
     }
     __syncthreads();
     for (int i = tid; i < n; i += blockDim.x) {
-        const int e = ids[i];
+        const int e = COHERENT ? __ldcg(ids + i) : ids[i];
         if (e >= 0 && e < E) {
             const int pos = atomicAdd(&cursor[e], 1);
             rows[pos] = i / k;
@@ -390,6 +391,82 @@ router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restric
     permute_block(reinterpret_cast<int*>(smem), ids, T_ * k, k, E, offsets, rows_out, dest, err);
 }
 
+// A few dozen tokens (17 to 48): logits, choice and grouping in ONE launch, one block per token.  Warp v
+// takes the rows v, v + 8, ... of the router's matrix (each logit the same sum in the same order as in
+// router_logits_kernel), warp 0 then chooses for the token, and the block that finishes last groups the pairs by
+// expert (the counter of router_fused_kernel: launches of the two must not overlap either).
+constexpr int TOKEN_WARPS = 8;      // (16 warps a token: no faster)
+
+template <typename TX, typename T, bool VEC>
+__global__ void __launch_bounds__(TOKEN_WARPS * 32)
+router_token_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
+                    float* logits, int32_t* ids, float* wts, float* gate, int32_t* offsets, int32_t* rows_out,
+                    int32_t* dest, int T_, int H, int E, int k, int norm, int has_gate, int score_fn, float scale,
+                    const float* __restrict__ select_bias, int* err) {
+    extern __shared__ float smem[];            // [H] the token, then [2 (E + 1)] for the choice
+    __shared__ float scratch[32];
+    __shared__ int s_last;
+    const int rows = E + (has_gate ? 1 : 0);
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (blockIdx.x < 4)        // a few blocks ask for the whole matrix; the others find it in L2
+        for (int e = (int)blockIdx.x * TOKEN_WARPS + warp; e < rows; e += 4 * TOKEN_WARPS)
+            prefetch_row_l2(w + (long long)e * H, H, lane);
+    dep_wait();
+    dep_launch_next();
+    float* x = smem;
+    // the sum of squares in router_logits_kernel's order: its 256 threads' partial sums, the other warps add zeros
+    float ss = 0.f;
+    if (tid < ROUTER_THREADS)
+        for (int i = tid; i < H; i += ROUTER_THREADS) {
+            const float v = to_f32(h[(long long)t * H + i]);
+            x[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    if (norm_w != nullptr) {
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+        for (int i = tid; i < H; i += blockDim.x) x[i] = (x[i] * inv) * norm_w[i];
+    }
+    __syncthreads();
+    for (int e = warp; e < rows; e += TOKEN_WARPS) {
+        const T* wr = w + (long long)e * H;
+        float s = 0.f;
+        if (VEC) {
+#pragma unroll 4
+            for (int b = 0; b < H; b += 256) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int i = b + 128 * half + lane * 4;
+                    if (i < H) {
+                        float wv[4];
+                        load4(wr + i, wv);
+                        const float4 xa = *reinterpret_cast<const float4*>(x + i);
+                        s = fmaf(xa.x, wv[0], s); s = fmaf(xa.y, wv[1], s); s = fmaf(xa.z, wv[2], s); s = fmaf(xa.w, wv[3], s);
+                    }
+                }
+            }
+        } else {
+            for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
+        }
+        s = warp_sum(s);
+        if (lane == 0) logits[(long long)t * rows + e] = s;
+    }
+    __syncthreads();
+    if (warp == 0)
+        select_token<false>(smem + H, logits, ids, wts, gate, t, E, k, norm, has_gate, score_fn, scale, select_bias);
+    // the last block to get here groups the pairs of all tokens
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        s_last = atomicAdd(&g_router_blocks_done, 1u) == gridDim.x - 1 ? 1 : 0;
+        if (s_last) g_router_blocks_done = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    permute_block<true>(reinterpret_cast<int*>(smem), ids, T_ * k, k, E, offsets, rows_out, dest, err);
+}
+
 }  // namespace
 
 void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
@@ -453,25 +530,45 @@ void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int3
     check_launch("moe_permute");
 }
 
-void router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
+int router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
                          float* wts, float* gate, int32_t* offsets, int32_t* rows_out, int32_t* dest, int T, int H,
                          int E, int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,
                          const float* select_bias, cudaStream_t stream) {
-    if (T <= 0) return;
+    if (T <= 0) return 0;
     const int rows = E + (has_gate ? 1 : 0);
     const size_t need = sizeof(float) * (size_t)H;
     const size_t need2 = sizeof(float) * (size_t)ROUTER_WARPS * 2 * (E + 1);
     const size_t smem = need > need2 ? need : need2;
-    if (T > 16 || smem > 200 * 1024 || E > 4096) {
+    const size_t smem_token = sizeof(float) * ((size_t)H + 2 * (size_t)(E + 1));
+    // (measured, 60 experts of 2,048: 24 / 32 / 48 tokens 3 % / 2 % / 2 % faster a decode step than the three
+    // launches, 64 tokens 1.4 % slower: a block then reads the whole matrix for one token, on 64 multiprocessors)
+    const bool per_token = T > 16 && T <= 48 && smem_token <= 200 * 1024 && E <= 4096;
+    if ((T > 16 && !per_token) || smem > 200 * 1024 || E > 4096) {
         router_topk(h, w, norm_w, eps, logits, ids, wts, gate, T, H, E, k, norm, has_gate, dtype, h_is_f32, score_fn,
                     scale, select_bias, stream);
         moe_permute(ids, T * k, k, E, offsets, rows_out, dest, stream);
-        return;
+        return 3;
     }
     DLM_CHECK(E >= 1 && k >= 1 && k <= E, "router: top-k must be in 1..num_experts");
     DLM_CHECK(score_fn == 0 || score_fn == 1, "router: score function must be 0 (softmax) or 1 (sigmoid)");
     const bool x32 = norm_w != nullptr || h_is_f32 != 0;
     const bool vec = H % 8 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+    if (per_token) {
+#define DLM_ROUTER_TOKEN(TX, TW, VEC)                                                                         \
+    {                                                                                                         \
+        auto kern = router_token_kernel<TX, TW, VEC>;                                                         \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_token);             \
+        launch_dep(kern, T, TOKEN_WARPS * 32, smem_token, stream, static_cast<const TX*>(h),                  \
+                   static_cast<const TW*>(w), norm_w, eps, logits, ids, wts, gate, offsets, rows_out, dest, T, H, E, \
+                   k, norm, has_gate, score_fn, scale, select_bias, error_flag_ptr());                        \
+    }
+        if (dtype == F32) { if (vec) DLM_ROUTER_TOKEN(float, float, true) else DLM_ROUTER_TOKEN(float, float, false) }
+        else if (x32) { if (vec) DLM_ROUTER_TOKEN(float, __nv_bfloat16, true) else DLM_ROUTER_TOKEN(float, __nv_bfloat16, false) }
+        else { if (vec) DLM_ROUTER_TOKEN(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER_TOKEN(__nv_bfloat16, __nv_bfloat16, false) }
+#undef DLM_ROUTER_TOKEN
+        check_launch("router_token");
+        return 1;
+    }
     dim3 grid(T, (rows + ROUTER_WARPS - 1) / ROUTER_WARPS);
 #define DLM_ROUTER_FUSED(TX, TW, VEC)                                                                         \
     {                                                                                                         \
@@ -486,6 +583,7 @@ void router_topk_permute(const void* h, const void* w, const float* norm_w, floa
     else { if (vec) DLM_ROUTER_FUSED(__nv_bfloat16, __nv_bfloat16, true) else DLM_ROUTER_FUSED(__nv_bfloat16, __nv_bfloat16, false) }
 #undef DLM_ROUTER_FUSED
     check_launch("router_fused");
+    return 1;
 }
 
 }  // namespace dlmk

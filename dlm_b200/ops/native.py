@@ -229,7 +229,7 @@ class NativeOps:
     def route(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
               select_bias=None):
         """``router_topk`` and ``moe_permute`` together: ``(ids, wts, gate, offsets, rows, dest)``.  A step
-        of at most 16 tokens does all of it in one launch."""
+        of at most 48 tokens does all of it in one launch."""
         T, H = h.shape
         assert w.shape == (E + (1 if has_gate else 0), H)
         assert h.dtype in (w.dtype, torch.float32) and (norm_weight is None or h.dtype == torch.float32)
@@ -243,8 +243,7 @@ class NativeOps:
         offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
         rows = torch.empty((T * k,), dtype=torch.int32, device=dev)
         dest = torch.empty((T, k), dtype=torch.int32, device=dev)
-        self.launches += 1 if T <= 16 else 3
-        self.k.router_topk_permute(_p(h), _p(w), _p(norm_weight), float(eps), _p(logits), _p(ids), _p(wts), _p(gate),
+        self.launches += self.k.router_topk_permute(_p(h), _p(w), _p(norm_weight), float(eps), _p(logits), _p(ids), _p(wts), _p(gate),
                                    _p(offsets), _p(rows), _p(dest), T, H, E, k, int(norm), int(has_gate),
                                    _dt(w.dtype), h_is_f32, score_fn, float(scale), _p(select_bias), self._stream())
         return ids, wts, gate, offsets, rows, dest

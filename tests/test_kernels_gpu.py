@@ -192,10 +192,11 @@ def test_router_score_functions(ops, ref, dtype, E, k, H, norm, score, scale, bi
         assert not torch.equal(plain[0], want[0])
 
 
-@pytest.mark.parametrize("T", [1, 8, 37, 64, 65, 700])
-@pytest.mark.parametrize("E,k,H,gate", [(60, 4, 2048, True), (12, 3, 256, False), (64, 8, 3584, True), (5, 1, 72, False)])
+@pytest.mark.parametrize("T", [1, 8, 16, 17, 37, 48, 49, 64, 700])
+@pytest.mark.parametrize("E,k,H,gate", [(60, 4, 2048, True), (12, 3, 256, False), (64, 8, 3584, True), (5, 1, 72, False),
+                                        (130, 6, 100, False)])
 def test_route_in_one_launch_equals_the_separate_kernels(ops, T, E, k, H, gate):
-    """Logits, choice and grouping together (one launch up to 64 tokens) give what the separate kernels give,
+    """Logits, choice and grouping together (one launch up to 48 tokens, of two kinds) give what the separate kernels give,
     bit for bit, also when called again and again (the launch counts its blocks in a global counter)."""
     x = rand((T, H), torch.float32, 27, 2.0)
     nw = 1 + rand((H,), torch.float32, 28, 0.1)
