@@ -35,11 +35,12 @@ void gemm_mma(const void* a, int lda, const int32_t* a_rows, const void* w, int 
 
 // tcgen05 / TMA kernel for many rows of A (bfloat16 inputs, rows of A contiguous: no gather).  gemm_tc returns
 // false when the tensor maps cannot be made (the caller then takes another kernel).
-// Grouped products go to the tcgen05 kernel from one and a half rows per expert on average.  (Measured on a
-// decode step of 60 experts, top 4, rows of 2,048 and 1,408 elements: 64 rows over the experts are faster on
-// the streaming kernel, 3,390 against 3,230 tok/s; 96 rows on this one, 3,930 against 3,690; 256 rows 7,820
-// against 7,180; 64 experts, top 8, rows of 3,584 elements, 512 rows: 3,015 against 1,980.)
-inline bool grouped_rows_are_many(long long M, long long num_experts) { return 2 * M > 3 * num_experts; }
+// Grouped products go to the tcgen05 kernel from a little more than one row per expert on average.  (Measured
+// on a decode step of 60 experts, top 4, rows of 2,048 and 1,408 elements, tok/s on the streaming kernel against
+// this one: 56 rows over the experts 3,106 : 2,945; 64 rows 3,390 : 3,204; 72 rows 3,325 : 3,440; 80 rows
+// 3,394 : 3,493; 96 rows 3,690 : 3,930; 256 rows 7,180 : 8,010.  64 experts, top 8, rows of 3,584 elements, 512
+// rows: 1,980 : 3,140.)
+inline bool grouped_rows_are_many(long long M, long long num_experts) { return 8 * M > 9 * num_experts; }
 bool gemm_tc_enabled();
 bool gemm_tc_ok(const void* a, int lda, const void* w, int ldw, long long w_expert_stride, int M, int N, int K,
                 int in_dtype);

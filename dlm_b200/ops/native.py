@@ -150,9 +150,9 @@ class NativeOps:
         E, N, K = w_gate_up.shape
         M = rows.numel()
         out = torch.empty((M, N // 2), dtype=a.dtype, device=a.device)
-        if (self.fast and self.tc and a.dtype == torch.bfloat16 and 2 * M > 3 * E and K % 8 == 0
+        if (self.fast and self.tc and a.dtype == torch.bfloat16 and 8 * M > 9 * E and K % 8 == 0
                 and a.stride(0) == K):
-            # more than a row or two per expert: put each expert's rows side by side, so that the TMA can fetch them as tiles
+            # more than about a row per expert (the kernels' own rule): put each expert's rows side by side, so that the TMA can fetch them as tiles
             gathered = torch.empty((M, K), dtype=a.dtype, device=a.device)
             self.launches += 1
             self.k.gather_rows(_p(a), _p(rows), _p(gathered), M, K, _dt(a.dtype), self._stream())

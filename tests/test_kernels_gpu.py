@@ -297,15 +297,15 @@ def test_rope_identity_at_zero_and_norm(ops):
     (6, 2048 + 512, 96, [40, 0, 1, 0, 3, 2]),      # one expert far above the mean: several passes over its rows
     (4, 5632, 64, [0, 17, 0, 5]),                  # rows longer than one stage: chunks of K
     (3, 264, 1408, [9, 9, 9]),
-    # at most one and a half rows per expert on average (the weight-streaming kernel's share), one expert with
+    # at most 1.125 rows per expert on average (the weight-streaming kernel's share), one expert with
     # many: its rows go in passes of 8; rows of two chunks (held in registers) and of three (fetched per chunk)
     (40, 2560, 96, [30] + [0] * 30 + [1] * 9),
     (40, 5632, 64, [0] * 20 + [21] + [1] * 19),
-    (40, 1408, 264, [2, 0, 0, 19] + [1] * 36),
+    (40, 1408, 264, [2, 0, 0, 19] + [1] * 20 + [0] * 16),
 ])
 def test_grouped_products_skewed(ops, ref, E, H, I, counts):
     """Rows very unevenly spread over the experts, experts without rows among them, on both grouped kernels (the
-    tcgen05 kernel from one and a half rows per expert on average, the weight-streaming kernel below)."""
+    tcgen05 kernel from 1.125 rows per expert on average, the weight-streaming kernel below)."""
     dtype = torch.bfloat16
     M = sum(counts)
     offsets = torch.tensor([0] + torch.tensor(counts).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
