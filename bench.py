@@ -414,9 +414,10 @@ def run_sweep(args, pk) -> dict:
 
 
 def run_kernels(pk) -> dict:
-    """The weight-streaming product alone, timed with CUDA events inside a captured graph, the weights rotated
-    over several copies so that L2 does not hold them: the decode step's shapes (8 rows), the routed experts'
-    products at 1 / 8 / 64 tokens, and 8 rows against 256 MB of weights with rows of 512 to 4,096 elements."""
+    """The decode step's products alone, timed with CUDA events inside a captured graph, the weights rotated
+    over several copies so that L2 does not hold them: the dense shapes (8 rows, the weight-streaming kernel), the
+    routed experts' products at 1 / 8 / 64 tokens (whichever kernel the rule chooses: the weight-streaming one at
+    1 and 8, the tcgen05 one at 64), and 8 rows against 256 MB of weights with rows of 512 to 4,096 elements."""
     import torch
 
     from dlm_b200.ops import native_ops
@@ -443,7 +444,7 @@ def run_kernels(pk) -> dict:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1000 / (5 * reps * copies)
 
-    out = {"metric": "weight-streaming product alone: us and TB/s", "peak_gbs": pk["hbm_gbs"], "dense": {},
+    out = {"metric": "the decode step's products alone: us and TB/s", "peak_gbs": pk["hbm_gbs"], "dense": {},
            "grouped": {}, "row_length": {}}
     for (N, K, kind) in [(6144, 2048, "store"), (2048, 2048, "add"), (11264, 2048, "swiglu"), (2048, 5632, "store"),
                          (151936, 2048, "store")]:
