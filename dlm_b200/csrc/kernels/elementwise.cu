@@ -121,8 +121,33 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut
         }
         return acc;
     };
+    // VEC: a thread's first NORM_KEEP groups of four stay in registers between the two passes (rows of up to
+    // 1,024 NORM_KEEP columns are read once), and so do their weights, asked for before the sum is known
+    constexpr int NORM_KEEP = 4;
+    float4 kept[NORM_KEEP], wk[NORM_KEEP];
     float part = 0.f;
-    for (int i = 32 * warp + lane; i < items; i += 256) part = square(i, part);
+    if (VEC) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+        for (int n = 0; n < NORM_KEEP; ++n) {
+            const int i = (int)threadIdx.x + 256 * n;
+            kept[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+            wk[n] = kept[n];
+            if (i < items) { kept[n] = x4[i]; wk[n] = __ldg(w4 + i); }
+        }
+#pragma unroll
+        for (int n = 0; n < NORM_KEEP; ++n) {
+            const int i = (int)threadIdx.x + 256 * n;
+            if (i < items) {
+                const float4 v = kept[n];
+                part = fmaf(v.x, v.x, part); part = fmaf(v.y, v.y, part); part = fmaf(v.z, v.z, part); part = fmaf(v.w, v.w, part);
+            }
+        }
+        for (int i = (int)threadIdx.x + 256 * NORM_KEEP; i < items; i += 256) part = square(i, part);
+    } else {
+        for (int i = 32 * warp + lane; i < items; i += 256) part = square(i, part);
+    }
     part = warp_sum(part);
     if (lane == 0) s_part[warp] = part;
     __syncthreads();
@@ -130,16 +155,23 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, TOut
 #pragma unroll
     for (int v = 0; v < 8; ++v) ss += s_part[v];
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-    const int first = threadIdx.x, step = 256;
     if (VEC) {
         const float4* x4 = reinterpret_cast<const float4*>(xr);
         const float4* w4 = reinterpret_cast<const float4*>(w);
-        for (int i = first; i < items; i += step) {
+#pragma unroll
+        for (int n = 0; n < NORM_KEEP; ++n) {
+            const int i = (int)threadIdx.x + 256 * n;
+            if (i < items) {
+                const float4 v = kept[n], g = wk[n];
+                Out4<TOut>::store(o + 4 * i, (v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
+            }
+        }
+        for (int i = (int)threadIdx.x + 256 * NORM_KEEP; i < items; i += 256) {
             const float4 v = x4[i], g = __ldg(w4 + i);
             Out4<TOut>::store(o + 4 * i, (v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
         }
     } else {
-        for (int i = first; i < items; i += step) o[i] = from_f32<TOut>((xr[i] * inv) * w[i]);
+        for (int i = (int)threadIdx.x; i < items; i += 256) o[i] = from_f32<TOut>((xr[i] * inv) * w[i]);
     }
 }
 
