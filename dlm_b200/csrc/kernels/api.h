@@ -42,7 +42,8 @@ void gather_rows(const void* src, const int32_t* rows, void* out, int n_rows, in
 // Rotates q and k heads of qkv[T, (nh + 2 nkv) * hd] (f32) by position * inv_freq within the first rotary_dim
 // dims (pair i is dims (i, i + rotary_dim / 2), or (2i, 2i + 1) with interleaved != 0; inv_freq == nullptr: no
 // rotation), writes q to q_out[T, nh * hd] and, where slots != nullptr and slots[t] >= 0, k and v to the paged
-// caches [pages, nkv, page_size, hd].
+// caches [pages, nkv, page_size, hd].  positions, slots and inv_freq are read before the kernel launched just
+// before this one has ended (they are a step's inputs): that kernel must not be the one that writes them.
 void rope_kv_write(const float* qkv, const int32_t* positions, const float* inv_freq, int rotary_dim, int interleaved,
                    const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int T, int nh, int nkv, int hd,
                    int page_size, int total_pages, int dtype, cudaStream_t stream);

@@ -260,8 +260,8 @@ __global__ void rope_kv_write_vec_kernel(const float* qkv, const int32_t* __rest
                                          T* v_cache, int nh, int nkv, int hd, int page_size, int total_pages,
                                          int* err) {
     extern __shared__ float sc[];                  // [2][rotary_dim / 2]: sines, cosines
-    dep_wait();
-    dep_launch_next();
+    // Positions, slots and frequencies are the step's inputs, not a kernel's output: the angles are ready
+    // before the kernel that writes q, k and v has ended.
     const int t = blockIdx.x;
     const int Q = nh * hd, KV = nkv * hd;
     const float* row = qkv + (long long)t * (Q + 2 * KV);
@@ -269,13 +269,14 @@ __global__ void rope_kv_write_vec_kernel(const float* qkv, const int32_t* __rest
     const int half = inv_freq != nullptr ? rotary_dim / 2 : 0;
     const int rd = 2 * half;
     int in_page = 0, page = -1;
+    bool bad_slot = false;
     if (slots != nullptr) {
         const int s = slots[t];
         if (s >= 0) {
             page = s / page_size;
             in_page = s % page_size;
             if (page >= total_pages) {
-                if (threadIdx.x == 0) *err = 2;
+                bad_slot = true;
                 page = -1;
             }
         }
@@ -286,6 +287,9 @@ __global__ void rope_kv_write_vec_kernel(const float* qkv, const int32_t* __rest
         sc[i] = sn;
         sc[half + i] = cs;
     }
+    dep_wait();
+    dep_launch_next();
+    if (bad_slot && threadIdx.x == 0) *err = 2;
     __syncthreads();
     const int rot_heads = nh + nkv;
     const int tpt = blockDim.x * gridDim.y, tid0 = blockIdx.y * blockDim.x + threadIdx.x;
