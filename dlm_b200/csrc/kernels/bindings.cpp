@@ -60,12 +60,13 @@ PYBIND11_MODULE(_dlm_kernels, m) {
     });
     m.def("router_topk_permute", [](u64 h, u64 w, u64 norm_w, float eps, u64 logits, u64 ids, u64 wts, u64 gate,
                                     u64 offsets, u64 rows, u64 dest, int T, int H, int E, int k, int norm, int has_gate,
-                                    int dtype, int h_is_f32, int score_fn, float scale, u64 select_bias, u64 stream) {
+                                    int dtype, int h_is_f32, int score_fn, float scale, u64 select_bias, int x_settled,
+                                    u64 stream) {
         return dlmk::router_topk_permute(ptr<const void>(h), ptr<const void>(w), ptr<const float>(norm_w), eps,
                                   ptr<float>(logits), ptr<int32_t>(ids), ptr<float>(wts), ptr<float>(gate),
                                   ptr<int32_t>(offsets), ptr<int32_t>(rows), ptr<int32_t>(dest), T, H, E, k, norm,
                                   has_gate, dtype, h_is_f32, score_fn, scale, ptr<const float>(select_bias),
-                                  st(stream));
+                                  x_settled, st(stream));
     });
     m.def("moe_permute", [](u64 ids, int n, int k, int E, u64 offsets, u64 rows, u64 dest, u64 stream) {
         dlmk::moe_permute(ptr<const int32_t>(ids), n, k, E, ptr<int32_t>(offsets), ptr<int32_t>(rows),

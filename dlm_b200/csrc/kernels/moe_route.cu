@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(ROUTER_THREADS)
 router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w, float eps,
                     float* logits, int32_t* ids, float* wts, float* gate, int32_t* offsets, int32_t* rows_out,
                     int32_t* dest, int T_, int H, int E, int k, int norm, int has_gate, int score_fn, float scale,
-                    const float* __restrict__ select_bias, int* err) {
+                    const float* __restrict__ select_bias, int x_settled, int* err) {
     extern __shared__ float smem[];
     __shared__ float scratch[32];
     __shared__ int s_last;
@@ -333,8 +333,12 @@ router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restric
         const int e_mine = blockIdx.y * ROUTER_WARPS + (threadIdx.x >> 5);
         if (e_mine < rows) prefetch_row_l2(w + (long long)e_mine * H, H, threadIdx.x & 31);
     }
-    dep_wait();
-    dep_launch_next();
+    // x_settled: the activations are older than the kernel launched just before this one (the caller says so),
+    // and the logits are worked out while that kernel ends; nothing is written before the wait.
+    if (!x_settled) {
+        dep_wait();
+        dep_launch_next();
+    }
     float* x = smem;            // [H]
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float ss = 0.f;
@@ -350,9 +354,9 @@ router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restric
     }
     __syncthreads();
     const int e = blockIdx.y * ROUTER_WARPS + warp;
+    float s = 0.f;
     if (e < rows) {
         const T* wr = w + (long long)e * H;
-        float s = 0.f;
         if (VEC) {
 #pragma unroll 4
             for (int b = 0; b < H; b += 256) {
@@ -371,8 +375,12 @@ router_fused_kernel(const TX* h, const T* __restrict__ w, const float* __restric
             for (int i = lane; i < H; i += 32) s = fmaf(x[i], to_f32(wr[i]), s);
         }
         s = warp_sum(s);
-        if (lane == 0) __stcg(logits + (long long)t * rows + e, s);
     }
+    if (x_settled) {
+        dep_wait();
+        dep_launch_next();
+    }
+    if (e < rows && lane == 0) __stcg(logits + (long long)t * rows + e, s);
     // the last block to get here does the rest
     __threadfence();
     __syncthreads();
@@ -411,6 +419,7 @@ router_token_kernel(const TX* h, const T* __restrict__ w, const float* __restric
     if (blockIdx.x < 4)        // a few blocks ask for the whole matrix; the others find it in L2
         for (int e = (int)blockIdx.x * TOKEN_WARPS + warp; e < rows; e += 4 * TOKEN_WARPS)
             prefetch_row_l2(w + (long long)e * H, H, lane);
+    // (working the logits out before the wait, as router_fused_kernel does, was slower here: 1 % of a step)
     dep_wait();
     dep_launch_next();
     float* x = smem;
@@ -533,7 +542,7 @@ void moe_permute(const int32_t* ids, int n, int k, int E, int32_t* offsets, int3
 int router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
                          float* wts, float* gate, int32_t* offsets, int32_t* rows_out, int32_t* dest, int T, int H,
                          int E, int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,
-                         const float* select_bias, cudaStream_t stream) {
+                         const float* select_bias, int x_settled, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int rows = E + (has_gate ? 1 : 0);
     const size_t need = sizeof(float) * (size_t)H;
@@ -576,7 +585,7 @@ int router_topk_permute(const void* h, const void* w, const float* norm_w, float
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
         launch_dep(kern, grid, ROUTER_THREADS, smem, stream, static_cast<const TX*>(h),                       \
                    static_cast<const TW*>(w), norm_w, eps, logits, ids, wts, gate, offsets, rows_out, dest, T, H, E, \
-                   k, norm, has_gate, score_fn, scale, select_bias, error_flag_ptr());                        \
+                   k, norm, has_gate, score_fn, scale, select_bias, x_settled, error_flag_ptr());             \
     }
     if (dtype == F32) { if (vec) DLM_ROUTER_FUSED(float, float, true) else DLM_ROUTER_FUSED(float, float, false) }
     else if (x32) { if (vec) DLM_ROUTER_FUSED(float, __nv_bfloat16, true) else DLM_ROUTER_FUSED(float, __nv_bfloat16, false) }

@@ -227,9 +227,11 @@ class NativeOps:
         return ids, wts, gate
 
     def route(self, h, w, E, k, norm, has_gate, norm_weight=None, eps=0.0, score="softmax", scale=1.0,
-              select_bias=None):
+              select_bias=None, input_settled=False):
         """``router_topk`` and ``moe_permute`` together: ``(ids, wts, gate, offsets, rows, dest)``.  A step
-        of at most 48 tokens does all of it in one launch."""
+        of at most 48 tokens does all of it in one launch.  ``input_settled``: ``h`` was not written by the
+        kernel launched just before this call (it is a step's residual and a norm kernel ran in between); a
+        step of few tokens then works its logits out while that kernel ends."""
         T, H = h.shape
         assert w.shape == (E + (1 if has_gate else 0), H)
         assert h.dtype in (w.dtype, torch.float32) and (norm_weight is None or h.dtype == torch.float32)
@@ -245,7 +247,8 @@ class NativeOps:
         dest = torch.empty((T, k), dtype=torch.int32, device=dev)
         self.launches += self.k.router_topk_permute(_p(h), _p(w), _p(norm_weight), float(eps), _p(logits), _p(ids), _p(wts), _p(gate),
                                    _p(offsets), _p(rows), _p(dest), T, H, E, k, int(norm), int(has_gate),
-                                   _dt(w.dtype), h_is_f32, score_fn, float(scale), _p(select_bias), self._stream())
+                                   _dt(w.dtype), h_is_f32, score_fn, float(scale), _p(select_bias),
+                                                   int(bool(input_settled)), self._stream())
         return ids, wts, gate, offsets, rows, dest
 
     def moe_permute(self, ids, E):

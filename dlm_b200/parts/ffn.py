@@ -108,8 +108,11 @@ class SoftmaxTopKMoE(FeedForward):
         # router logits (and the shared expert's gate) from the 32-bit normalised residual: an RMS norm is
         # applied again inside the router's kernel, any other norm is asked for a 32-bit result
         if rms is not None:
+            # (the residual was last written before ``pre_norm`` ran: the kernel launched just before this
+            # one, the norm's or the shared expert's, only reads it)
             ids, wts, gate, offsets, rows, dest = ops.route(resid, self.w_router, self.E, self.k, self.norm,
-                                                            self.has_gate, norm_weight=rms[0], eps=rms[1])
+                                                            self.has_gate, norm_weight=rms[0], eps=rms[1],
+                                                            input_settled=True)
         else:
             x = h if pre_norm is None else pre_norm.forward(resid, ctx.rt, out_dtype=torch.float32)
             ids, wts, gate, offsets, rows, dest = ops.route(x, self.w_router, self.E, self.k, self.norm, self.has_gate)

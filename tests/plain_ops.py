@@ -160,7 +160,7 @@ class PlainOps:
             wts = torch.where(s > 0, wts / s, wts)
         return ids.to(torch.int32), wts * scale, gate
 
-    def route(self, h, w, E, k, norm, has_gate, **kw):
+    def route(self, h, w, E, k, norm, has_gate, input_settled=False, **kw):
         ids, wts, gate = self.router_topk(h, w, E, k, norm, has_gate, **kw)
         return (ids, wts, gate) + tuple(self.moe_permute(ids, E))
 

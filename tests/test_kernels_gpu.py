@@ -203,8 +203,9 @@ def test_route_in_one_launch_equals_the_separate_kernels(ops, T, E, k, H, gate):
     w = rand((E + int(gate), H), torch.bfloat16, 29, 0.3)
     ids, wts, g = ops.router_topk(x, w, E, k, True, gate, norm_weight=nw, eps=1e-6)
     off, rows, dest = ops.moe_permute(ids, E)
-    for _ in range(3):
-        i2, w2, g2, off2, rows2, dest2 = ops.route(x, w, E, k, True, gate, norm_weight=nw, eps=1e-6)
+    for settled in (False, True, True):      # settled: the logits are worked out before the dependency wait
+        i2, w2, g2, off2, rows2, dest2 = ops.route(x, w, E, k, True, gate, norm_weight=nw, eps=1e-6,
+                                                   input_settled=settled)
         assert torch.equal(ids, i2) and torch.equal(wts, w2) and torch.equal(off, off2)
         if gate:
             assert torch.equal(g, g2)
