@@ -67,14 +67,14 @@ size_t attention_scratch_floats(int R, int nh, int nkv, int hd, int max_kv_len);
 // logits: scratch of T * (E + has_gate) floats (the router logits are left there).
 void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
                  float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
-                 int score_fn, float scale, const float* select_bias, cudaStream_t stream);
+                 int score_fn, float scale, const float* select_bias, int x_settled, cudaStream_t stream);
 
 // router_topk followed by moe_permute (below).  One launch up to 16 tokens (blocks of 8 experts per token, the
 // block that finishes last chooses for every token and groups) and from 17 to 48 tokens (a block per token
 // computes all its logits and chooses; the last block groups); three launches from 49 tokens on.  Returns the
 // number of launches.  x_settled != 0: `h` was written before the kernel launched just before this one began its
-// work (a step's residual, with a norm kernel in between): the logits of a few tokens are then worked out while
-// that kernel ends.
+// work (a step's residual, with a norm kernel in between): the logits of at most 16 tokens, or the first of 512
+// and more, are then worked out while that kernel ends (`router_topk` takes the same flag).
 int router_topk_permute(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids,
                          float* wts, float* gate, int32_t* offsets, int32_t* rows, int32_t* dest, int T, int H, int E,
                          int k, int norm, int has_gate, int dtype, int h_is_f32, int score_fn, float scale,

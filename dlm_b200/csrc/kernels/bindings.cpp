@@ -56,7 +56,7 @@ PYBIND11_MODULE(_dlm_kernels, m) {
                             u64 select_bias, u64 stream) {
         dlmk::router_topk(ptr<const void>(h), ptr<const void>(w), ptr<const float>(norm_w), eps, ptr<float>(logits),
                           ptr<int32_t>(ids), ptr<float>(wts), ptr<float>(gate), T, H, E, k, norm, has_gate, dtype,
-                          h_is_f32, score_fn, scale, ptr<const float>(select_bias), st(stream));
+                          h_is_f32, score_fn, scale, ptr<const float>(select_bias), 0, st(stream));
     });
     m.def("router_topk_permute", [](u64 h, u64 w, u64 norm_w, float eps, u64 logits, u64 ids, u64 wts, u64 gate,
                                     u64 offsets, u64 rows, u64 dest, int T, int H, int E, int k, int norm, int has_gate,

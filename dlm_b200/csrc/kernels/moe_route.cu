@@ -100,10 +100,15 @@ constexpr int ROUTER_EW = 4;     // experts per warp in the many-token kernel
 template <typename TX, typename T>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __restrict__ norm_w,
-                           float eps, float* logits, int T_, int H, int rows) {
+                           float eps, float* logits, int T_, int H, int rows, int x_settled) {
     extern __shared__ float smem[];               // [ROUTER_TB][H]
-    dep_wait();
-    dep_launch_next();
+    // x_settled: the activations are older than the kernel launched just before this one; the tokens are
+    // staged and a warp's first sums worked out while that kernel ends, and nothing is stored before the wait
+    bool waited = x_settled == 0;
+    if (waited) {
+        dep_wait();
+        dep_launch_next();
+    }
     const int t0 = blockIdx.x * ROUTER_TB, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = min(ROUTER_TB, T_ - t0);
     // Staging: warp j brings token t0 + j into shared memory and normalises it.  The sum of squares is taken
@@ -173,6 +178,11 @@ router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __
                 }
             }
         }
+        if (!waited) {
+            dep_wait();
+            dep_launch_next();
+            waited = true;
+        }
 #pragma unroll
         for (int a = 0; a < ROUTER_EW; ++a)
 #pragma unroll
@@ -180,6 +190,10 @@ router_logits_multi_kernel(const TX* h, const T* __restrict__ w, const float* __
                 const float v = warp_sum(s[a][j]);
                 if (lane == 0 && j < nt && e0 + a < rows) logits[(long long)(t0 + j) * rows + e0 + a] = v;
             }
+    }
+    if (!waited) {
+        dep_wait();
+        dep_launch_next();
     }
 }
 
@@ -480,7 +494,7 @@ router_token_kernel(const TX* h, const T* __restrict__ w, const float* __restric
 
 void router_topk(const void* h, const void* w, const float* norm_w, float eps, float* logits, int32_t* ids, float* wts,
                  float* gate, int T, int H, int E, int k, int norm, int has_gate, int dtype, int h_is_f32,
-                 int score_fn, float scale, const float* select_bias, cudaStream_t stream) {
+                 int score_fn, float scale, const float* select_bias, int x_settled, cudaStream_t stream) {
     if (T <= 0) return;
     DLM_CHECK(score_fn == 0 || score_fn == 1, "router: score function must be 0 (softmax) or 1 (sigmoid)");
     const bool x32 = norm_w != nullptr || h_is_f32 != 0;      // the activations are 32-bit whatever the weights are
@@ -499,7 +513,7 @@ void router_topk(const void* h, const void* w, const float* norm_w, float eps, f
         auto kern = router_logits_multi_kernel<TX, TW>;                                                       \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_multi);             \
         launch_dep(kern, mgrid, ROUTER_THREADS, smem_multi, stream, static_cast<const TX*>(h),                \
-                   static_cast<const TW*>(w), norm_w, eps, logits, T, H, rows);                               \
+                   static_cast<const TW*>(w), norm_w, eps, logits, T, H, rows, x_settled);                    \
     }
         if (dtype == F32) DLM_ROUTER_MULTI(float, float)
         else if (x32) DLM_ROUTER_MULTI(float, __nv_bfloat16)
@@ -554,7 +568,7 @@ int router_topk_permute(const void* h, const void* w, const float* norm_w, float
     const bool per_token = T > 16 && T <= 48 && smem_token <= 200 * 1024 && E <= 4096;
     if ((T > 16 && !per_token) || smem > 200 * 1024 || E > 4096) {
         router_topk(h, w, norm_w, eps, logits, ids, wts, gate, T, H, E, k, norm, has_gate, dtype, h_is_f32, score_fn,
-                    scale, select_bias, stream);
+                    scale, select_bias, x_settled, stream);
         moe_permute(ids, T * k, k, E, offsets, rows_out, dest, stream);
         return 3;
     }
