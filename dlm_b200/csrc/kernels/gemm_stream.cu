@@ -85,15 +85,24 @@ __device__ __forceinline__ void mma_free(float (&c)[4], uint32_t a0, uint32_t a1
 
 struct Work { int expert, row0, m_count, tile; };
 
+// The experts that have rows, in ascending order, with their rows: filled once per block, so that a tile costs
+// no load from global memory before its copy can be asked for.
+struct ActiveExperts {
+    int expert[MAX_ACTIVE];
+    int row0[MAX_ACTIVE];
+    int count[MAX_ACTIVE];
+};
+
 // Item `item` of the launch: dense, tile `item` for all rows of A; grouped, tile item % tiles of the
 // (item / tiles)-th expert that has rows.
-__device__ __forceinline__ Work get_work(const StreamParams& p, const int* s_active, int item) {
+__device__ __forceinline__ Work get_work(const StreamParams& p, const ActiveExperts& act, int item) {
     Work wk{0, 0, p.M, item};
     if (p.expert_offsets != nullptr) {
-        wk.expert = s_active[item / p.tiles];
-        wk.tile = item % p.tiles;
-        wk.row0 = p.expert_offsets[wk.expert];
-        wk.m_count = min(p.expert_offsets[wk.expert + 1], p.M) - wk.row0;
+        const int slot = item / p.tiles;
+        wk.tile = item - slot * p.tiles;
+        wk.expert = act.expert[slot];
+        wk.row0 = act.row0[slot];
+        wk.m_count = act.count[slot];
     }
     return wk;
 }
@@ -106,7 +115,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
     __shared__ __align__(8) uint64_t empty_bar[STAGES];    // all consumer warps have read a stage
     __shared__ __align__(8) uint64_t red_full[2];          // partial sums of a tile written by all consumer warps
     __shared__ __align__(8) uint64_t red_empty[2];         // ... and added up and stored: the buffer is free again
-    __shared__ int s_active[MAX_ACTIVE];
+    __shared__ ActiveExperts s_active;
     __shared__ int s_n_active, s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -135,10 +144,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_kernel(StreamParams p)
             int seen = 0;
             for (int base = 0; base < p.num_experts; base += 32) {
                 const int e = base + lane;
-                const bool has = e < p.num_experts && min(p.expert_offsets[e + 1], p.M) > p.expert_offsets[e];
+                const int first = e < p.num_experts ? p.expert_offsets[e] : 0;
+                const int count = e < p.num_experts ? min(p.expert_offsets[e + 1], p.M) - first : 0;
+                const bool has = count > 0;
                 const unsigned mask = __ballot_sync(0xffffffffu, has);
                 const int slot = seen + __popc(mask & ((1u << lane) - 1));
-                if (has && slot < MAX_ACTIVE) s_active[slot] = e;
+                if (has && slot < MAX_ACTIVE) {
+                    s_active.expert[slot] = e;
+                    s_active.row0[slot] = first;
+                    s_active.count[slot] = count;
+                }
                 seen += __popc(mask);
             }
             if (lane == 0) s_n_active = min(seen, MAX_ACTIVE);
