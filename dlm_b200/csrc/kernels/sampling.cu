@@ -9,7 +9,8 @@
 // number always give the same token.  A bucket's 64-bit sum is kept as two 32-bit words, added
 // with the hardware's 32-bit shared-memory atomics and an explicit carry (a 64-bit atomic add
 // on shared memory is a compare-and-swap loop, and the first passes put the whole vocabulary
-// into a handful of buckets: that loop was most of the kernel's four milliseconds).
+// into a handful of buckets: that loop was most of the kernel's four milliseconds).  A row of a large
+// vocabulary is shared by the blocks of a cluster, see team_rank() below.
 #include "api.h"
 #include "common.cuh"
 
@@ -18,11 +19,46 @@ namespace dlmk {
 namespace {
 
 constexpr int THREADS = 1024;
+constexpr int SAMPLE_TEAM = 8;          // most blocks that share a row of a large vocabulary
 
 __device__ __forceinline__ unsigned int desc_key(float v) {
     unsigned int u = __float_as_uint(v);
     u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);   // ascending order of floats
     return ~u;                                        // larger float -> smaller key
+}
+
+// A row's candidates are shared out over a TEAM: the blocks of a thread-block cluster (one block when the
+// vocabulary is small).  A block keeps its partial results in its own shared memory; after a cluster barrier
+// every block reads all the partial results (distributed shared memory) and combines them in the same order,
+// so all blocks of a team reach the same decisions without a word being sent back.
+__device__ __forceinline__ unsigned int team_rank() {
+    unsigned int r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned int team_size() {
+    unsigned int r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void team_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// reads of what block `rank` of the team holds at `p` (an address in this block's own shared memory)
+__device__ __forceinline__ uint32_t team_addr(const void* p, unsigned int rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ unsigned int team_load_u32(const void* p, unsigned int rank) {
+    unsigned int v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(team_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long team_load_u64(const void* p, unsigned int rank) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(team_addr(p, rank)) : "memory");
+    return v;
 }
 
 // (max value, first index holding it) over the block; result valid in every thread.
@@ -115,12 +151,33 @@ struct RowView {
     int idx_bits;
     float mx, inv_temp, minp_thr;
     unsigned long long cut;   // candidates have composite key <= cut
+    unsigned int rank, team;  // this block's place in its team, the team's size
+    bool vec;             // V is a multiple of 4 and z is 16-byte aligned: the row is read four logits at a time
     __device__ unsigned long long ckey(int i, float v) const {
         return ((unsigned long long)desc_key(v) << idx_bits) | (unsigned long long)i;
     }
     __device__ float prob(float v) const { return expf((v - mx) * inv_temp); }
     __device__ unsigned long long mass(float p) const { return (unsigned long long)((double)p * 1099511627776.0); }
 };
+
+// Calls f(i, z[i]) for the elements of the row that this thread of this block of the team takes.  A pass over the row is bound by the
+// latency of its loads (one block reads 600 KB): 16-byte loads, four of them in flight, not one logit at a time.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const RowView& rv, F f) {
+    const int first = (int)(rv.rank * blockDim.x + threadIdx.x), step = (int)(rv.team * blockDim.x);
+    if (rv.vec) {
+        const float4* z4 = reinterpret_cast<const float4*>(rv.z);
+        const int n4 = rv.V >> 2;
+#pragma unroll 4
+        for (int j = first; j < n4; j += step) {
+            const float4 v = z4[j];
+            f(4 * j, v.x); f(4 * j + 1, v.y); f(4 * j + 2, v.z); f(4 * j + 3, v.w);
+        }
+    } else {
+#pragma unroll 4
+        for (int i = first; i < rv.V; i += step) f(i, rv.z[i]);
+    }
+}
 
 __device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
 #pragma unroll
@@ -140,29 +197,34 @@ __device__ __forceinline__ void bucket_add(unsigned int* lo, unsigned int* hi, i
     if (up != 0u) atomicAdd(&hi[b], up);
 }
 
-// Sum of masses (or count) of the candidates.
-__device__ unsigned long long block_total(const RowView& rv, bool count, unsigned long long* s_part) {
+// Sum of masses (or count) of the candidates, over the team.  `s_part`: 33 words; [32] is the block's sum, which
+// the other blocks read.
+__device__ unsigned long long team_total(const RowView& rv, bool count, unsigned long long* s_part) {
     unsigned long long local = 0ull;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < rv.V; i += blockDim.x) {
-        const float v = rv.z[i];
+    for_each_logit(rv, [&](int i, float v) {
         const float p = rv.prob(v);
         if (rv.ckey(i, v) <= rv.cut && p >= rv.minp_thr) local += count ? 1ull : rv.mass(p);
-    }
+    });
     local = warp_sum_u64(local);
     __syncthreads();
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = local;
     __syncthreads();
-    unsigned long long r = 0ull;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) r += s_part[w];
-    __syncthreads();
-    return r;
+    if (threadIdx.x == 0) {
+        unsigned long long r = 0ull;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) r += s_part[w];
+        s_part[32] = r;
+    }
+    team_sync();
+    unsigned long long total = 0ull;
+    for (unsigned int c = 0; c < rv.team; ++c) total += team_load_u64(&s_part[32], c);
+    team_sync();                 // everyone has read before anyone writes the slots again
+    return total;
 }
 
 // Composite key of the first candidate (in key order) at which the running count / mass reaches `target`.
 __device__ unsigned long long block_select(const RowView& rv, int mode, unsigned long long target,
                                            unsigned int* bucket_lo, unsigned int* bucket_hi,
-                                           unsigned long long* s_state) {
+                                           unsigned long long* merged, unsigned long long* s_state) {
     const int total_bits = 32 + rv.idx_bits;
     const int passes = (total_bits + 7) / 8;
     unsigned long long prefix = 0ull, before = 0ull;
@@ -170,23 +232,29 @@ __device__ unsigned long long block_select(const RowView& rv, int mode, unsigned
         const int shift = (passes - 1 - pass) * 8;
         for (int b = threadIdx.x; b < 256; b += blockDim.x) { bucket_lo[b] = 0u; bucket_hi[b] = 0u; }
         __syncthreads();
-#pragma unroll 4
-        for (int i = threadIdx.x; i < rv.V; i += blockDim.x) {
-            const float v = rv.z[i];
+        for_each_logit(rv, [&](int i, float v) {
             const unsigned long long ck = rv.ckey(i, v);
-            if (ck > rv.cut) continue;
-            if (pass > 0 && (ck >> (shift + 8)) != (prefix >> (shift + 8))) continue;
+            if (ck > rv.cut) return;
+            if (pass > 0 && (ck >> (shift + 8)) != (prefix >> (shift + 8))) return;
             const float p = rv.prob(v);
-            if (p < rv.minp_thr) continue;
+            if (p < rv.minp_thr) return;
             bucket_add(bucket_lo, bucket_hi, (int)((ck >> shift) & 255ull), mode == COUNT ? 1ull : rv.mass(p));
+        });
+        // every block of the team adds up all the blocks' buckets and scans the sums: the same answer everywhere
+        team_sync();
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            unsigned long long sum = 0ull;
+            for (unsigned int c = 0; c < rv.team; ++c)
+                sum += ((unsigned long long)team_load_u32(&bucket_hi[b], c) << 32) | team_load_u32(&bucket_lo[b], c);
+            merged[b] = sum;
         }
-        __syncthreads();
+        team_sync();                 // all reads of the buckets are done: the next pass may clear them
         if (threadIdx.x == 0) {
             unsigned long long run = before;
             int pick = -1, last = -1;
             unsigned long long last_sum = 0ull;
             for (int b = 0; b < 256; ++b) {
-                const unsigned long long sum = ((unsigned long long)bucket_hi[b] << 32) | bucket_lo[b];
+                const unsigned long long sum = merged[b];
                 if (sum == 0ull) continue;
                 last = b;
                 last_sum = sum;
@@ -217,9 +285,13 @@ sample_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ unsigned int bucket_lo[256], bucket_hi[256];
+    __shared__ unsigned long long merged[256];
     __shared__ unsigned long long s_state[2];
-    __shared__ unsigned long long s_part[32];
-    const int row = blockIdx.x;
+    __shared__ unsigned long long s_part[33];
+    __shared__ float s_best_v;
+    __shared__ int s_best_i;
+    const unsigned int rank = team_rank(), team = team_size();
+    const int row = (int)(blockIdx.x / team);
     const float temperature = params[row * 4 + 0], top_p = params[row * 4 + 1], min_p = params[row * 4 + 2],
                 penalty = params[row * 4 + 3];
     const float* lg = logits + (long long)row * V;
@@ -227,36 +299,50 @@ sample_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
     const float* z = lg;
     if (penalty != 1.0f && seen_offsets != nullptr) {
         float* zc = scratch + (long long)row * V;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) zc[i] = lg[i];
-        __syncthreads();
-        for (int s = seen_offsets[row] + threadIdx.x; s < seen_offsets[row + 1]; s += blockDim.x) {
+        const int first = (int)(rank * blockDim.x + threadIdx.x), step = (int)(team * blockDim.x);
+        for (int i = first; i < V; i += step) zc[i] = lg[i];
+        __threadfence();
+        team_sync();
+        for (int s = seen_offsets[row] + first; s < seen_offsets[row + 1]; s += step) {
             const int t = seen_tokens[s];
             if (t >= 0 && t < V) {
-                const float v = zc[t];
+                const float v = __ldcg(zc + t);     // (not through L1: the line holds other blocks' elements too,
+                                                    //  which they may be changing, and this block reads it later)
                 zc[t] = v > 0.f ? v / penalty : v * penalty;
             }
         }
-        __syncthreads();
+        __threadfence();
+        team_sync();
         z = zc;
     }
-    // the maximum and its first index (the greedy answer)
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = z[i];
-        if (v > bv) { bv = v; bi = i; }
-    }
-    float mx;
-    int mi;
-    block_argmax(bv, bi, sv, si, mx, mi);
-    if (mi == 0x7fffffff) mi = 0;
-    if (!(temperature > 0.f)) {
-        if (threadIdx.x == 0) out[row] = mi;
-        return;
-    }
+    // the maximum and its first index (the greedy answer): per block, then over the team
     RowView rv;
     rv.z = z;
     rv.V = V;
+    rv.rank = rank;
+    rv.team = team;
+    rv.vec = (V & 3) == 0 && (reinterpret_cast<uintptr_t>(z) & 15) == 0;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for_each_logit(rv, [&](int i, float v) {
+        if (v > bv) { bv = v; bi = i; }         // a thread's indices ascend: the first maximum stays
+    });
+    float mx;
+    int mi;
+    block_argmax(bv, bi, sv, si, mx, mi);
+    if (threadIdx.x == 0) { s_best_v = mx; s_best_i = mi; }
+    team_sync();
+    for (unsigned int c = 0; c < team; ++c) {
+        const float ov = __uint_as_float(team_load_u32(&s_best_v, c));
+        const int oi = (int)team_load_u32(&s_best_i, c);
+        if (ov > mx || (ov == mx && oi < mi)) { mx = ov; mi = oi; }
+    }
+    team_sync();
+    if (mi == 0x7fffffff) mi = 0;
+    if (!(temperature > 0.f)) {                 // (the same for every block of the team)
+        if (threadIdx.x == 0 && rank == 0) out[row] = mi;
+        return;
+    }
     rv.idx_bits = 1;
     while ((1 << rv.idx_bits) < V) ++rv.idx_bits;
     rv.mx = mx;
@@ -264,18 +350,18 @@ sample_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V
     rv.minp_thr = 0.f;
     rv.cut = ~0ull;
     const int k = top_k[row];
-    if (k > 0 && k < V) rv.cut = block_select(rv, COUNT, (unsigned long long)k, bucket_lo, bucket_hi, s_state);
+    if (k > 0 && k < V) rv.cut = block_select(rv, COUNT, (unsigned long long)k, bucket_lo, bucket_hi, merged, s_state);
     if (top_p > 0.f && top_p < 1.f) {
-        const unsigned long long Z = block_total(rv, false, s_part);
+        const unsigned long long Z = team_total(rv, false, s_part);
         unsigned long long target = (unsigned long long)((double)top_p * (double)Z);
         if (target < 1ull) target = 1ull;
-        rv.cut = block_select(rv, MASS_GE, target, bucket_lo, bucket_hi, s_state);
+        rv.cut = block_select(rv, MASS_GE, target, bucket_lo, bucket_hi, merged, s_state);
     }
     if (min_p > 0.f) rv.minp_thr = fminf(min_p, 1.0f);   // the top candidate (probability 1 before scaling) stays
-    const unsigned long long Z = block_total(rv, false, s_part);
+    const unsigned long long Z = team_total(rv, false, s_part);
     const unsigned long long target = (unsigned long long)((double)u[row] * (double)Z);
-    const unsigned long long pick = block_select(rv, MASS_GT, target, bucket_lo, bucket_hi, s_state);
-    if (threadIdx.x == 0) {
+    const unsigned long long pick = block_select(rv, MASS_GT, target, bucket_lo, bucket_hi, merged, s_state);
+    if (threadIdx.x == 0 && rank == 0) {
         int tok = (int)(pick & ((1ull << rv.idx_bits) - 1ull));
         if (tok >= V) tok = mi;
         out[row] = tok;
@@ -306,7 +392,25 @@ void sample(const float* logits, int32_t* out, int N, int V, const float* params
             cudaStream_t stream) {
     if (N <= 0) return;
     DLM_CHECK(V > 0 && V <= (1 << 30), "sample: vocabulary size out of range");
-    sample_kernel<<<N, THREADS, 0, stream>>>(logits, out, V, params, top_k, u, seen_offsets, seen_tokens, scratch);
+    // a large vocabulary is shared out over a cluster of blocks (one block walks 150,000 logits in 26 us a pass,
+    // and a draw takes nine passes)
+    // (as many blocks a row as leave the rows of one launch a block each at the same time: 64 rows with 8 blocks
+    // each took longer than with one)
+    int team = 1;
+    if (V >= 32768)
+        while (team < SAMPLE_TEAM && (long long)N * team * 2 <= sm_count()) team *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)N * team);
+    cfg.blockDim = dim3(THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = team;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, sample_kernel, logits, out, V, params, top_k, u, seen_offsets, seen_tokens, scratch);
     check_launch("sample");
 }
 

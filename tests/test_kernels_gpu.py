@@ -448,7 +448,8 @@ def test_sampler_against_plain(ops, ref, V):
                           device="cuda")
     top_k = torch.tensor([0, 0, 0, 0, 0, 50, 1, 0, 7, 0, 0, 20], dtype=torch.int32, device="cuda")
     seen_offsets = torch.arange(0, 4 * (N + 1), 4, dtype=torch.int32, device="cuda")
-    seen_tokens = torch.arange(4 * N, dtype=torch.int32, device="cuda") % V
+    # spread over the vocabulary, so that with a large one the blocks that share a row penalise each other's parts
+    seen_tokens = ((torch.arange(4 * N, dtype=torch.int64, device="cuda") * 37123) % V).to(torch.int32)
     agree = total = 0
     for trial in range(6):
         u = torch.rand((N,), generator=torch.Generator().manual_seed(trial)).cuda()
