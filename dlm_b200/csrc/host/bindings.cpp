@@ -1,4 +1,5 @@
 // Python bindings of the host runtime (cache manager and scheduler).
+#include <algorithm>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -81,6 +82,32 @@ PYBIND11_MODULE(_dlm_host, m) {
                  c.pack(items, lay, reinterpret_cast<int32_t*>(out));
              },
              py::arg("items"), py::arg("layout"), py::arg("out_ptr"), py::arg("capacity"))
+        .def("pack_decode",
+             // a step in which every request brings one token and wants its logits: `pack` without the items
+             [](const CacheManager& c, const std::vector<int>& slots, const std::vector<int32_t>& tokens,
+                const StepLayout& lay, uintptr_t out, size_t capacity) {
+                 if ((size_t)lay.total > capacity) throw std::invalid_argument("metadata buffer is too small");
+                 if (slots.size() != tokens.size() || (int)slots.size() > lay.num_requests ||
+                     lay.num_tokens != lay.num_requests || lay.num_wanted != lay.num_requests)
+                     throw std::invalid_argument("the step does not fit the fixed metadata layout");
+                 std::vector<StepItem> items(slots.size());
+                 for (size_t i = 0; i < slots.size(); ++i) {
+                     items[i].slot = slots[i];
+                     items[i].tokens.assign(1, tokens[i]);
+                     items[i].want.assign(1, 0);
+                     for (int g = 0; g < c.num_groups(); ++g)
+                         if ((int)c.table(slots[i], g).size() > lay.table_width[g])
+                             throw std::invalid_argument("a request's block table is wider than the layout's");
+                 }
+                 c.pack(items, lay, reinterpret_cast<int32_t*>(out));
+             },
+             py::arg("slots"), py::arg("tokens"), py::arg("layout"), py::arg("out_ptr"), py::arg("capacity"))
+        .def("max_length",
+             [](const CacheManager& c, const std::vector<int>& slots) {
+                 int m = 0;
+                 for (int s : slots) m = std::max(m, c.length(s));
+                 return m;
+             })
         .def("check", &CacheManager::check);
 
     py::class_<SchedulerConfig>(m, "SchedulerConfig")

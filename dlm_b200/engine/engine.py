@@ -139,7 +139,8 @@ class Engine:
 
     # ------------------------------------------------- replayed decode steps
     def _run_decode(self, items):
-        """A pure decode step through its graph.  Returns (logits, greedy tokens) on the device.
+        """A pure decode step through its graph.  Returns (logits, greedy tokens) on the device and, from a
+        replayed graph, the greedy tokens in pinned host memory (valid once the stream has been waited for).
 
         A graph is the step function and the arg-max over its logits for `rows` requests none of which
         holds more than `bucket` tokens; everything its kernels read that changes from step to step lies
@@ -148,7 +149,8 @@ class Engine:
         capture) and its result is the step's result; the graph is then recorded for the steps after it.
         Recording runs nothing, so every step runs exactly once, which per-request state needs."""
         cache, ops = self.cache, self.rt.ops
-        longest = max(cache.manager.length(s) for s, _, _ in items)
+        slots = [int(s) for s, _, _ in items]
+        longest = cache.manager.max_length(slots)
         bucket = 256
         while bucket < longest:
             bucket *= 2
@@ -158,14 +160,19 @@ class Engine:
         rows = len(items)
         padded = _row_bucket(rows, self.cache.num_slots)
         key = (padded, bucket)
-        sitems = [cache.host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
         ent = self._graphs.get(key)
         if ent is not None:
+            # the graph copies the metadata from its pinned buffer itself and leaves the tokens in another; the
+            # step before this one has been waited for (its tokens were read), so the buffers are free
             self._graphs.move_to_end(key)
-            cache.fill_metadata(sitems, ent["layout"], ent["meta"])
+            stage = ent["stage"]
+            cache.manager.pack_decode(slots, [int(t[0]) for _, t, _ in items], ent["layout"], stage.data_ptr(),
+                                      stage.numel())
+            cache.last_h2d_bytes = 4 * ent["layout"].total
             ent["graph"].replay()
             ops.launches += ent["launches"]
-            return ent["logits"][:rows], ent["tokens"][:rows]
+            return ent["logits"][:rows], ent["tokens"][:rows], ent["host_tokens"][:rows]
+        sitems = [cache.host.StepItem(int(s), list(t), list(w)) for s, t, w in items]
         width = -(-self.max_context // min(cache.group_page_size))
         lay = cache.manager.plan_layout(sitems, width, padded)
         meta = torch.zeros(lay.total, dtype=torch.int32, device=self.rt.device)
@@ -180,16 +187,20 @@ class Engine:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
+        stage = torch.empty(lay.total, dtype=torch.int32).pin_memory()
+        host_tokens = torch.empty(padded, dtype=torch.int32).pin_memory()
         with torch.cuda.graph(graph, pool=self._graph_pool):
+            meta.copy_(stage, non_blocking=True)
             g_logits = self.model.step(batch, cache)
             g_tokens = ops.argmax(g_logits)
+            host_tokens.copy_(g_tokens, non_blocking=True)
         self.graphs_recorded += 1
         self.graph_record_seconds += time.perf_counter() - t_rec
         while len(self._graphs) >= self.max_graphs:
             self._graphs.popitem(last=False)
         self._graphs[key] = dict(graph=graph, layout=lay, meta=meta, logits=g_logits, tokens=g_tokens,
-                                 launches=ops.launches - before, width=width)
-        return logits[:rows], tokens[:rows]
+                                 launches=ops.launches - before, width=width, stage=stage, host_tokens=host_tokens)
+        return logits[:rows], tokens[:rows], None
 
     # ------------------------------------------------------------- generation
     def submit(self, prompt: Iterable[int], params: SamplingParams | None = None, max_new_tokens: int = 16,
@@ -216,22 +227,33 @@ class Engine:
         every token produced."""
         sched = self.scheduler
         plan = sched.plan()
-        if not plan.items:
+        pitems = plan.items          # (a copy of the plan's list: taken once)
+        if not pitems:
             fin = sched.drain_finished()
             self._deliver(fin)
             if not fin and not plan.preempted and sched.has_work():
                 raise RuntimeError("the scheduler could not place any request")
             return []
-        for it in plan.items:
+        items, rows, pure_decode = [], [], True
+        for it in pitems:
+            toks = it.tokens
             if it.start == 0:
                 self.cache.reset_state(it.slot)
-        items = [(it.slot, it.tokens, [len(it.tokens) - 1] if it.sample else []) for it in plan.items]
-        rows = [it for it in plan.items if it.sample]
+            if it.sample:
+                rows.append(it)
+                items.append((it.slot, toks, [len(toks) - 1]))
+            else:
+                items.append((it.slot, toks, []))
+            pure_decode = pure_decode and it.sample and len(toks) == 1
         samplers = [self._samplers[it.id] for it in rows]
-        if self.use_graphs and all(len(it.tokens) == 1 and it.sample for it in plan.items):
-            logits, greedy = self._run_decode(items)
+        if self.use_graphs and pure_decode:
+            logits, greedy, on_host = self._run_decode(items)
             if all(s.params.plain_greedy for s in samplers):
-                tokens = greedy.tolist()
+                if on_host is not None:
+                    torch.cuda.current_stream().synchronize()
+                    tokens = on_host.tolist()
+                else:
+                    tokens = greedy.tolist()
             else:
                 tokens = sample_rows(self.rt.ops, logits, samplers)
         else:
@@ -239,8 +261,8 @@ class Engine:
             tokens = sample_rows(self.rt.ops, logits, samplers)
         self.last_logits = logits
         self.rt.ops.check_errors()
-        for it, tok in zip(rows, tokens):
-            self._samplers[it.id].note(tok)
+        for smp, tok in zip(samplers, tokens):
+            smp.note(tok)
         self._deliver(sched.commit(plan, tokens))
         return [(it.id, tok) for it, tok in zip(rows, tokens)]
 

@@ -195,6 +195,22 @@ def test_padded_rows_belong_to_nobody():
         assert rows[:2].tolist() == ref[plain.off_table[g]:plain.off_table[g] + 2 * w].reshape(2, w).tolist()
         assert rows[2].tolist() == [pages] + [-1] * (w - 1) and rows[3].tolist() == rows[2].tolist()
     assert m.check() == ""
+    # a pure decode step packed from two arrays gives the same words, and refuses what the layout cannot hold
+    fast = np.full(lay.total, -7, dtype=np.int32)
+    m.pack_decode([a, b], [7, 9], lay, fast.ctypes.data, fast.size)
+    assert fast.tolist() == buf.tolist()
+    assert m.max_length([a, b]) == 41 and m.max_length([b]) == 4
+    with pytest.raises(ValueError):
+        m.pack_decode([a, b], [7], lay, fast.ctypes.data, fast.size)
+    narrow = m.plan_layout(items, 0, 4)
+    assert narrow.table_width[0] == 4
+    c = m.open()
+    for _ in range(4):
+        m.append([(c, 20)])                    # 80 tokens in portions (the windowed group gives pages back):
+    with pytest.raises(ValueError):            # five pages, wider than the layout planned without it (four)
+        m.pack_decode([a, c], [7, 9], narrow, fast.ctypes.data, fast.size)
+    with pytest.raises(ValueError):
+        m.pack_decode([a, b], [7, 9], lay, fast.ctypes.data, 3)
 
 
 def test_row_buckets():
