@@ -26,6 +26,9 @@ void rmsnorm(const float* x, const float* w, void* out, const int32_t* rows, int
 // Grouped: rows [expert_offsets[e], expert_offsets[e+1]) use W + e * w_expert_stride elements.
 // a_rows (optional) gathers the rows of A: row m of the product reads A[a_rows[m], :].
 // `fast` != 0 allows tensor-core kernels (bfloat16 inputs only); 0 forces the plain FMA kernel.
+// expert_offsets are read before the kernel launched just before this one has ended (the tensor-core kernel lists
+// its tiles while it is set up): that kernel must not be the one that writes them (in a layer a gather or the
+// experts' first product lies in between).
 void gemm(const void* a, int lda, const int32_t* a_rows, const void* w, int ldw, long long w_expert_stride,
           const int32_t* expert_offsets, int num_experts, const float* bias, void* out, int ldo, int M, int N, int K,
           int in_dtype, int out_dtype, int epilogue, int fast, cudaStream_t stream);
