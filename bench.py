@@ -224,7 +224,7 @@ class Measurement:
     """One model on the device and the measurements taken on it: decode steps at several batch sizes
     (device time of the replayed step, and end to end through run_step) and one 2,048-token prefill."""
 
-    def __init__(self, raw, layers, prompt_len, context, max_batch, pk):
+    def __init__(self, raw, layers, prompt_len, context, max_batch, pk, page=64):
         import torch
 
         from dlm_b200.config import Qwen2MoeConfig
@@ -235,7 +235,7 @@ class Measurement:
         self.cfg = Qwen2MoeConfig.from_dict(raw)
         self.layers, self.prompt_len, self.pk = layers, prompt_len, pk
         torch.cuda.set_device(0)
-        self.page = 64
+        self.page = page
         pool_tokens = max_batch * (prompt_len + 256) + 4096
         t_load = time.time()
         self.eng = Engine.from_random(self.cfg, seed=0, dtype="bfloat16", page_size=self.page, max_tokens=pool_tokens,
@@ -532,6 +532,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--page-size", type=int, default=64, help="tokens per page of the cache (16, 32, 64, 128, ...)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (reported)")
     ap.add_argument("--layers-57b", type=int, default=None, help="layers of the larger model in `sizes_57b` (default: all "
                     "28 if they fit)")
@@ -572,7 +573,7 @@ def main() -> int:
         print(json.dumps(run_kernels(pk)))
         return 0
     max_batch = 64 if not args.no_points else args.batch
-    m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk)
+    m = Measurement(MODEL, args.layers, args.prompt_len, args.context, max_batch, pk, page=args.page_size)
     cfg = m.cfg
     if args.only_prefill:
         pre = m.prefill(2048, repeats=3)
