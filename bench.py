@@ -150,11 +150,12 @@ def run_serving(args) -> dict:
                max_window_layers=min(21, max(args.layers - 3, 0)), max_position_embeddings=32768)
     cfg = Qwen2MoeConfig.from_dict(raw)
     torch.cuda.set_device(0)
-    n_req, pool_tokens, max_context = 64, 262144, 16384 + 512 + 64
+    p_lo, p_hi = args.serving_prompts
+    n_req, pool_tokens, max_context = args.serving_requests, 262144, max(p_hi, 4096) + 512 + 64
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", page_size=64, max_tokens=pool_tokens,
                              max_requests=n_req, max_step_tokens=2048, max_context=max_context)
     gen = torch.Generator().manual_seed(4)
-    plen = torch.randint(256, 16385, (n_req,), generator=gen).tolist()
+    plen = torch.randint(p_lo, p_hi + 1, (n_req,), generator=gen).tolist()
     olen = torch.randint(64, 513, (n_req,), generator=gen).tolist()
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in plen]
     # warm-up: one short request end to end (kernels loaded, graphs of its shapes captured)
@@ -197,7 +198,7 @@ def run_serving(args) -> dict:
     st = eng.stats()
     ok = st["finished"] >= n_req and produced == sum(olen)
     line = {
-        "metric": "serving: generated tok/s, 64 requests, prompts 256-16384, outputs 64-512, continuous batching "
+        "metric": f"serving: generated tok/s, {n_req} requests, prompts {p_lo}-{p_hi}, outputs 64-512, continuous batching "
                   "(Qwen1.5-MoE-A2.7B sizes, layers 21-23 windowed at 4096, bf16, random weights)",
         "value": round(produced / (t1 - t0), 2), "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
         "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)", "impl": "ours",
@@ -533,6 +534,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--page-size", type=int, default=64, help="tokens per page of the cache (16, 32, 64, 128, ...)")
+    ap.add_argument("--serving-prompts", type=int, nargs=2, default=[256, 16384], metavar=("MIN", "MAX"),
+                    help="prompt lengths of the serving workload (uniform in MIN..MAX)")
+    ap.add_argument("--serving-requests", type=int, default=64, help="requests of the serving workload")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (reported)")
     ap.add_argument("--layers-57b", type=int, default=None, help="layers of the larger model in `sizes_57b` (default: all "
                     "28 if they fit)")
