@@ -437,8 +437,10 @@ def test_argmax_first_maximum(ops, ref):
     assert ops.argmax(big).tolist() == torch.argmax(big, dim=-1).tolist()
 
 
-@pytest.mark.parametrize("V", [301, 5000, 151936])
-def test_sampler_against_plain(ops, ref, V):
+@pytest.mark.parametrize("V,reps", [(301, 1), (5000, 1), (151936, 1), (151936, 2), (151936, 4), (40000, 7)])
+def test_sampler_against_plain(ops, ref, V, reps):
+    """``reps`` repeats the 12 rows: with a large vocabulary a row is shared by 8, 4, 2 or 1 blocks, the fewer the
+    more rows the launch has."""
     N = 12
     lg = rand((N, V), torch.float32, 53, 2.0)
     lg[3, 5] = lg[3, 100] = lg[3].max() + 1        # tied best candidates
@@ -450,15 +452,19 @@ def test_sampler_against_plain(ops, ref, V):
     seen_offsets = torch.arange(0, 4 * (N + 1), 4, dtype=torch.int32, device="cuda")
     # spread over the vocabulary, so that with a large one the blocks that share a row penalise each other's parts
     seen_tokens = ((torch.arange(4 * N, dtype=torch.int64, device="cuda") * 37123) % V).to(torch.int32)
+    if reps > 1:
+        lg, params, top_k = lg.repeat(reps, 1), params.repeat(reps, 1), top_k.repeat(reps)
+        seen_offsets = torch.arange(0, 4 * (N * reps + 1), 4, dtype=torch.int32, device="cuda")
+        seen_tokens = seen_tokens.repeat(reps)
     agree = total = 0
-    for trial in range(6):
-        u = torch.rand((N,), generator=torch.Generator().manual_seed(trial)).cuda()
+    for trial in range(6 if reps == 1 else 2):
+        u = torch.rand((N * reps,), generator=torch.Generator().manual_seed(trial)).cuda()
         got = ops.sample(lg, params, top_k, u, seen_offsets, seen_tokens)
         want = ref.sample(lg, params, top_k, u, seen_offsets, seen_tokens)
         agree += int((got == want).sum())
-        total += N
+        total += N * reps
         assert int(got[6]) == int(torch.argmax(lg[6]))          # top_k = 1 is greedy
-    assert agree >= total - 1          # a draw within rounding of a boundary may fall either way
+    assert agree >= total - reps       # a draw within rounding of a boundary may fall either way
 
 
 def test_repetition_penalty_hand_values(ops):
